@@ -1,0 +1,225 @@
+/*
+ * mcep - B200-native MoE expert-parallel dispatch / combine.
+ *
+ * C ABI of libmcep.so. Plain pointers and sizes only; every pointer that names
+ * tensor data is a CUDA device pointer owned by the caller, every `stream`
+ * argument is a `cudaStream_t` passed as an integer (0 = the default stream).
+ *
+ * The entry points are the ones a binding of Mooncake EP's `Buffer` needs; each
+ * comment names the reference interface it replaces (paths inside the Mooncake
+ * source tree).
+ *
+ * Errors: functions return MCEP_OK (0) or a negative code; `mcep_last_error()`
+ * then holds a message for the calling thread. Device-side anomalies never
+ * trap: they are recorded in a status word (`mcep_buffer_status`).
+ */
+#ifndef MCEP_H_
+#define MCEP_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MCEP_OK 0
+#define MCEP_ERR_INVALID (-1)   /* argument check failed (reference: EP_HOST_ASSERT) */
+#define MCEP_ERR_CUDA (-2)      /* a CUDA runtime call failed (reference: CUDA_CHECK) */
+#define MCEP_ERR_STATE (-3)     /* buffer not connected / peers not accessible */
+
+/* mooncake-ep/include/mooncake_ep_configs.cuh:5 (MAX_QP_COUNT), re-exported by
+ * the binding because the reference's Python bootstrap reads it. */
+#define MCEP_MAX_QP_COUNT 256
+/* Largest top-k per token. The reference allows 11
+ * (mooncake-ep/src/mooncake_ep_kernel.cu:487,773). */
+#define MCEP_MAX_TOPK 16
+/* Largest number of experts (flag slots reserved per direction). */
+#define MCEP_MAX_EXPERTS 4096
+/* An exported memory handle is a 64-byte cudaIpcMemHandle_t carried as 16
+ * int32, as in mooncake-transfer-engine/src/transport/device/
+ * p2p_device_transport.cpp:483-488. */
+#define MCEP_IPC_HANDLE_INT32S 16
+
+typedef struct mcep_buffer mcep_buffer;
+typedef struct mcep_event mcep_event;
+typedef struct mcep_hook mcep_hook;
+
+/* Message of the last failure on this thread ("" when none). */
+const char* mcep_last_error(void);
+
+/* Number of kernels this library has launched in this process (all buffers). */
+uint64_t mcep_kernel_launch_count(void);
+
+/* Measurement aid: while on, every kernel launch is bracketed by CUDA events on
+ * its own stream (kernels then run one after the other, never overlapped).
+ * `mcep_drain_kernel_times` waits for the recorded launches and writes one line
+ * per kernel, "name launches total_ms\n", NUL-terminated, then forgets them. */
+int mcep_set_kernel_timing(int on);
+int mcep_drain_kernel_times(char* out, size_t capacity);
+
+/*
+ * Bytes of symmetric memory a Buffer needs:
+ *   4*E*4 + 4*E*M*(32 + 2*H)
+ * Replaces mooncake::get_ep_buffer_size_hint / BufferPair
+ * (mooncake-ep/include/mooncake_ep_buffer.h:29-63,197-203); same value.
+ */
+uint64_t mcep_get_ep_buffer_size_hint(int num_max_dispatch_tokens_per_rank,
+                                      int hidden, int num_ranks,
+                                      int num_experts);
+
+/* ---- buffer life cycle ---------------------------------------------------
+ * Replaces MooncakeEpBuffer::MooncakeEpBuffer / ~MooncakeEpBuffer
+ * (mooncake-ep/src/mooncake_ep_buffer.cpp:74-191): allocates and zeroes the
+ * symmetric buffer and a 32 MiB workspace on the current device and creates a
+ * high-priority non-blocking communication stream. */
+int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes,
+                       int disable_p2p, mcep_buffer** out);
+int mcep_buffer_destroy(mcep_buffer* buf);
+
+/* mooncake-ep/include/mooncake_ep_buffer.h:135-151. There is no RDMA route in
+ * this library: ibgda_disabled() is always 1 and is_roce() always 0. */
+int mcep_buffer_ibgda_disabled(const mcep_buffer* buf);
+int mcep_buffer_p2p_enabled(const mcep_buffer* buf);
+int mcep_buffer_is_roce(const mcep_buffer* buf);
+/* 1 when every active rank's memory is mapped (single rank: always 1). */
+int mcep_buffer_use_fast_path(const mcep_buffer* buf);
+
+/* MooncakeEpBuffer::get_ipc_handle (mooncake_ep_buffer.cpp:518-521):
+ * writes MCEP_IPC_HANDLE_INT32S int32 to `out` (capacity in int32),
+ * `*n_written` = 0 when P2P is disabled. */
+int mcep_buffer_get_ipc_handle(mcep_buffer* buf, int32_t* out, int capacity,
+                               int* n_written);
+
+/* MooncakeEpBuffer::sync_nvlink_ipc_handles (mooncake_ep_buffer.cpp:523-529)
+ * and P2pDeviceTransportImpl::importPeerHandles
+ * (p2p_device_transport.cpp:491-715). `handles` is [num_ranks][n_per_handle]
+ * int32, `active_ranks_mask` is [num_ranks] (0 = do not map that rank). A later
+ * call replaces the earlier mapping (membership refresh). */
+int mcep_buffer_sync_nvlink_ipc_handles(mcep_buffer* buf,
+                                        const int32_t* handles,
+                                        int n_per_handle,
+                                        const int32_t* active_ranks_mask);
+
+/* In-process groups (several logical ranks in one process, e.g. tests that run
+ * the ranks one after the other on one GPU): hand the peers' base pointers over
+ * directly instead of through IPC handles. No counterpart in the reference. */
+int mcep_buffer_local_base(mcep_buffer* buf, void** base);
+int mcep_buffer_set_peer_bases(mcep_buffer* buf, void* const* bases,
+                               const int32_t* available);
+
+/* Options: "force_staged" (1 = a single rank also goes through the symmetric
+ * staging buffers and flags, as multi-rank groups do),
+ * "hard_timeout_ms" (upper bound applied to every device-side wait, also when
+ * timeout_us is -1; default 10000). */
+int mcep_buffer_set_option(mcep_buffer* buf, const char* name, int64_t value);
+
+/* Copies up to `n` int32 status words (0 = clean). Word 0: bit mask of
+ * anomalies (1 slot out of range, 2 hard wait bound hit, 4 bad source index). */
+int mcep_buffer_status(mcep_buffer* buf, int32_t* out, int n);
+
+/* ---- dispatch --------------------------------------------------------------
+ * Replaces MooncakeEpBuffer::dispatch
+ * (mooncake-ep/include/mooncake_ep_buffer.h:116-124,
+ *  mooncake-ep/src/mooncake_ep_buffer.cpp:193-339); argument meaning and
+ * checks as there. Outputs (caller-allocated):
+ *   packed_recv_x            [E/R][R*M][H]   e4m3 bytes (use_fp8) or bf16
+ *   packed_recv_x_scales     [E/R][H/128][R*M] fp32 storage (use_fp8 only)
+ *   packed_recv_count        [E/R] int32
+ *   packed_recv_src_info     [E/R][R*M] int32  token index at its source rank
+ *   packed_recv_layout_range [E/R][R] int64    (begin << 32) | count, 0 if empty
+ * Rows are ordered by source rank, then by token index. `active_ranks` [R]
+ * int32 is read AND written (a source that misses `timeout_us` is set to 0).
+ */
+typedef struct mcep_dispatch_args {
+    const void* x;              /* [num_tokens][hidden] bf16 */
+    const int64_t* topk_idx;    /* [num_tokens][num_topk], -1 = no expert */
+    int32_t* active_ranks;      /* [num_ranks] */
+    int32_t num_tokens;
+    int32_t hidden;
+    int32_t num_topk;
+    int32_t num_max_dispatch_tokens_per_rank;
+    int32_t num_experts;
+    int32_t use_fp8;
+    int64_t timeout_us;         /* -1: bounded only by "hard_timeout_ms" */
+    void* packed_recv_x;
+    float* packed_recv_x_scales;
+    int32_t* packed_recv_count;
+    int32_t* packed_recv_src_info;
+    int64_t* packed_recv_layout_range;
+    int32_t async_finish;       /* run on the communication stream, return an event */
+    int32_t return_recv_hook;   /* send now on `compute_stream`, receive in the hook */
+    uint64_t compute_stream;
+} mcep_dispatch_args;
+
+/* `*out_event` / `*out_hook` are set to NULL when the mode returns none
+ * (the reference returns std::nullopt there). */
+int mcep_dispatch(mcep_buffer* buf, const mcep_dispatch_args* args,
+                  mcep_event** out_event, mcep_hook** out_hook);
+
+/* ---- combine ---------------------------------------------------------------
+ * Replaces MooncakeEpBuffer::combine
+ * (mooncake-ep/include/mooncake_ep_buffer.h:126-133,
+ *  mooncake-ep/src/mooncake_ep_buffer.cpp:341-474).
+ *   x            [E/R][R*M][H] bf16 expert outputs in the packed layout
+ *   combined_x   [num_combined_tokens][H] bf16
+ * combined[t] = bf16( sum over k in order, fp32 FMA, of w[t][k] * x_row ),
+ * skipping topk_idx < 0 and experts whose owner rank is inactive.
+ */
+typedef struct mcep_combine_args {
+    const void* x;
+    const int64_t* topk_idx;
+    const float* topk_weights;
+    const int32_t* src_info;
+    const int64_t* layout_range;
+    int32_t* active_ranks;
+    int32_t num_local_experts;
+    int32_t num_combined_tokens;
+    int32_t hidden;
+    int32_t num_topk;
+    int32_t num_max_dispatch_tokens_per_rank;
+    int32_t num_experts;
+    int64_t timeout_us;
+    int32_t zero_copy;          /* must be 0 */
+    void* combined_x;
+    int32_t async_finish;
+    int32_t return_recv_hook;
+    uint64_t compute_stream;
+} mcep_combine_args;
+
+int mcep_combine(mcep_buffer* buf, const mcep_combine_args* args,
+                 mcep_event** out_event, mcep_hook** out_hook);
+
+/* ---- events and hooks --------------------------------------------------------
+ * mooncake-ep/include/mooncake_ep_event.h:9-44 (EventHandle) and the
+ * std::function returned by dispatch/combine. */
+int mcep_event_create(uint64_t stream, mcep_event** out); /* records on `stream` */
+int mcep_event_current_stream_wait(mcep_event* ev, uint64_t stream);
+int mcep_event_synchronize(mcep_event* ev);
+int mcep_event_free(mcep_event* ev);
+int mcep_hook_run(mcep_hook* hook);
+int mcep_hook_free(mcep_hook* hook);
+
+/* ---- routing layout ----------------------------------------------------------
+ * Per-expert and per-rank token counts, prefix offsets and the per-entry slot
+ * (position of a (token, expert) message among this rank's messages for that
+ * expert, token-ascending) from the top-k indices. The reference computes these
+ * inside its dispatch kernel with atomics in arrival order
+ * (mooncake-ep/src/mooncake_ep_kernel.cu:274,335-355); its deterministic
+ * counterpart is mooncake-ep/include/elastic/
+ * mooncake_ep_elastic_dispatch_deterministic_prologue.cuh:16-169.
+ *   count[E], rank_count[R], expert_prefix[E] (exclusive, inside the owner
+ *   rank's block), slot[T*K] (-1 for masked or repeated entries), all int32.
+ * `scratch` is at least mcep_routing_layout_scratch_bytes() of device memory,
+ * zeroed once before its first use; calls that share it must not overlap.
+ */
+size_t mcep_routing_layout_scratch_bytes(void);
+int mcep_routing_layout(const int64_t* topk_idx, int num_tokens, int num_topk,
+                        int num_experts, int num_ranks, int32_t* count,
+                        int32_t* rank_count, int32_t* expert_prefix,
+                        int32_t* slot, void* scratch, uint64_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MCEP_H_ */

@@ -1,0 +1,312 @@
+"""Native module of the package: the objects the reference exposes as
+`mooncake._ep` / `mooncake.ep` (mooncake-ep/src/ep_py.cpp:14-46,
+mooncake-wheel/mooncake/ep.py:1-26), bound with ctypes to the C ABI of
+`libmcep.so` (include/mcep.h).
+
+`Buffer`, `EventHandle`, `get_ep_buffer_size_hint` and `MAX_QP_COUNT` keep the
+reference's names, argument order and return shapes. There is no CPU path:
+if the shared library is missing it is built with nvcc, and if that fails the
+import fails.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Callable, List, Optional, Tuple
+
+from . import build as _build
+
+_c = ctypes
+
+
+class _DispatchArgs(_c.Structure):
+    _fields_ = [
+        ("x", _c.c_void_p), ("topk_idx", _c.c_void_p), ("active_ranks", _c.c_void_p),
+        ("num_tokens", _c.c_int32), ("hidden", _c.c_int32), ("num_topk", _c.c_int32),
+        ("num_max_dispatch_tokens_per_rank", _c.c_int32), ("num_experts", _c.c_int32),
+        ("use_fp8", _c.c_int32), ("timeout_us", _c.c_int64),
+        ("packed_recv_x", _c.c_void_p), ("packed_recv_x_scales", _c.c_void_p),
+        ("packed_recv_count", _c.c_void_p), ("packed_recv_src_info", _c.c_void_p),
+        ("packed_recv_layout_range", _c.c_void_p),
+        ("async_finish", _c.c_int32), ("return_recv_hook", _c.c_int32),
+        ("compute_stream", _c.c_uint64),
+    ]
+
+
+class _CombineArgs(_c.Structure):
+    _fields_ = [
+        ("x", _c.c_void_p), ("topk_idx", _c.c_void_p), ("topk_weights", _c.c_void_p),
+        ("src_info", _c.c_void_p), ("layout_range", _c.c_void_p), ("active_ranks", _c.c_void_p),
+        ("num_local_experts", _c.c_int32), ("num_combined_tokens", _c.c_int32),
+        ("hidden", _c.c_int32), ("num_topk", _c.c_int32),
+        ("num_max_dispatch_tokens_per_rank", _c.c_int32), ("num_experts", _c.c_int32),
+        ("timeout_us", _c.c_int64), ("zero_copy", _c.c_int32),
+        ("combined_x", _c.c_void_p),
+        ("async_finish", _c.c_int32), ("return_recv_hook", _c.c_int32),
+        ("compute_stream", _c.c_uint64),
+    ]
+
+
+def _load() -> ctypes.CDLL:
+    path = _build.LIB
+    if not os.path.exists(path):
+        path = _build.build()
+    L = ctypes.CDLL(path)
+    vp, i32, i64, u64 = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_uint64
+    sig = {
+        "mcep_last_error": (_c.c_char_p, []),
+        "mcep_kernel_launch_count": (u64, []),
+        "mcep_set_kernel_timing": (i32, [i32]),
+        "mcep_drain_kernel_times": (i32, [_c.c_char_p, _c.c_size_t]),
+        "mcep_get_ep_buffer_size_hint": (u64, [i32, i32, i32, i32]),
+        "mcep_buffer_create": (i32, [i32, i32, i64, i32, _c.POINTER(vp)]),
+        "mcep_buffer_destroy": (i32, [vp]),
+        "mcep_buffer_ibgda_disabled": (i32, [vp]),
+        "mcep_buffer_p2p_enabled": (i32, [vp]),
+        "mcep_buffer_is_roce": (i32, [vp]),
+        "mcep_buffer_use_fast_path": (i32, [vp]),
+        "mcep_buffer_get_ipc_handle": (i32, [vp, _c.POINTER(_c.c_int32), i32, _c.POINTER(i32)]),
+        "mcep_buffer_sync_nvlink_ipc_handles": (i32, [vp, _c.POINTER(_c.c_int32), i32,
+                                                      _c.POINTER(_c.c_int32)]),
+        "mcep_buffer_local_base": (i32, [vp, _c.POINTER(vp)]),
+        "mcep_buffer_set_peer_bases": (i32, [vp, _c.POINTER(vp), _c.POINTER(_c.c_int32)]),
+        "mcep_buffer_set_option": (i32, [vp, _c.c_char_p, i64]),
+        "mcep_buffer_status": (i32, [vp, _c.POINTER(_c.c_int32), i32]),
+        "mcep_dispatch": (i32, [vp, _c.POINTER(_DispatchArgs), _c.POINTER(vp), _c.POINTER(vp)]),
+        "mcep_combine": (i32, [vp, _c.POINTER(_CombineArgs), _c.POINTER(vp), _c.POINTER(vp)]),
+        "mcep_event_create": (i32, [u64, _c.POINTER(vp)]),
+        "mcep_event_current_stream_wait": (i32, [vp, u64]),
+        "mcep_event_synchronize": (i32, [vp]),
+        "mcep_event_free": (i32, [vp]),
+        "mcep_hook_run": (i32, [vp]),
+        "mcep_hook_free": (i32, [vp]),
+        "mcep_routing_layout_scratch_bytes": (_c.c_size_t, []),
+        "mcep_routing_layout": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, u64]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype, fn.argtypes = res, args
+    return L
+
+
+_lib = _load()
+
+MAX_QP_COUNT = 256  # mooncake-ep/include/mooncake_ep_configs.cuh:5
+
+
+def _check(rc: int) -> None:
+    """Failures surface as RuntimeError, as the reference's EPException does
+    through pybind (mooncake-ep/include/mooncake_ep_exception.cuh:12-24)."""
+    if rc != 0:
+        raise RuntimeError(_lib.mcep_last_error().decode())
+
+
+def kernel_launch_count() -> int:
+    return int(_lib.mcep_kernel_launch_count())
+
+
+def set_kernel_timing(on: bool) -> None:
+    _check(_lib.mcep_set_kernel_timing(1 if on else 0))
+
+
+def drain_kernel_times() -> dict:
+    """{kernel name: (launches, total milliseconds)} since timing was switched on."""
+    buf = _c.create_string_buffer(1 << 16)
+    _check(_lib.mcep_drain_kernel_times(buf, len(buf)))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms = line.split()
+        out[name] = (int(n), float(ms))
+    return out
+
+
+def get_ep_buffer_size_hint(num_max_dispatch_tokens_per_rank: int, hidden: int,
+                            num_ranks: int, num_experts: int) -> int:
+    """mooncake-ep/include/mooncake_ep_buffer.h:197-203."""
+    return int(_lib.mcep_get_ep_buffer_size_hint(num_max_dispatch_tokens_per_rank, hidden,
+                                                 num_ranks, num_experts))
+
+
+class EventHandle:
+    """mooncake-ep/include/mooncake_ep_event.h:9-44: a CUDA event recorded on
+    `stream_ptr` at construction."""
+
+    def __init__(self, stream_ptr: int = 0, _adopt: Optional[int] = None):
+        if _adopt is not None:
+            self._h = _c.c_void_p(_adopt)
+        else:
+            h = _c.c_void_p()
+            _check(_lib.mcep_event_create(stream_ptr, _c.byref(h)))
+            self._h = h
+
+    def current_stream_wait(self, stream_ptr: int) -> None:
+        _check(_lib.mcep_event_current_stream_wait(self._h, stream_ptr))
+
+    def synchronize(self) -> None:
+        _check(_lib.mcep_event_synchronize(self._h))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            _lib.mcep_event_free(h)
+
+
+class _Hook:
+    """The receive-phase callback (the `std::function<void()>` of the reference)."""
+
+    def __init__(self, handle: int):
+        self._h = _c.c_void_p(handle)
+
+    def __call__(self) -> None:
+        _check(_lib.mcep_hook_run(self._h))
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            _lib.mcep_hook_free(h)
+
+
+class Buffer:
+    """mooncake-ep/src/ep_py.cpp:28-46 / mooncake-ep/include/mooncake_ep_buffer.h:65-195."""
+
+    def __init__(self, rank: int, num_ranks: int, num_ep_buffer_bytes: int,
+                 disable_p2p: bool = False):
+        self._h = _c.c_void_p()
+        self.rank, self.num_ranks = rank, num_ranks
+        _check(_lib.mcep_buffer_create(rank, num_ranks, num_ep_buffer_bytes,
+                                       1 if disable_p2p else 0, _c.byref(self._h)))
+        self._dargs = _DispatchArgs()
+        self._cargs = _CombineArgs()
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            _lib.mcep_buffer_destroy(h)
+
+    # -- RDMA surface of the reference: there is no RDMA route here ------------
+    def ibgda_disabled(self) -> bool:
+        return True
+
+    def is_roce(self) -> bool:
+        return False
+
+    def update_local_qpns(self) -> None:
+        return None
+
+    def sync_ibgda_peers(self, *args) -> None:
+        return None
+
+    def get_mr_info(self) -> Tuple[int, int]:
+        return (0, 0)
+
+    def get_gid(self) -> Tuple[int, int]:
+        return (0, 0)
+
+    def get_local_qpns(self) -> List[int]:
+        return []
+
+    def get_local_lids(self) -> List[int]:
+        return []
+
+    # -- NVLink peer mapping ---------------------------------------------------
+    def p2p_enabled(self) -> bool:
+        return bool(_lib.mcep_buffer_p2p_enabled(self._h))
+
+    def use_fast_path(self) -> bool:
+        return bool(_lib.mcep_buffer_use_fast_path(self._h))
+
+    def get_ipc_handle(self) -> List[int]:
+        out = (_c.c_int32 * 16)()
+        n = _c.c_int(0)
+        _check(_lib.mcep_buffer_get_ipc_handle(self._h, out, 16, _c.byref(n)))
+        return list(out[: n.value])
+
+    def sync_nvlink_ipc_handles(self, remote_handles: List[List[int]],
+                                active_ranks_mask: List[int]) -> None:
+        n_per = max((len(h) for h in remote_handles), default=0)
+        if n_per == 0:
+            return
+        flat = (_c.c_int32 * (n_per * self.num_ranks))()
+        for r, h in enumerate(remote_handles[: self.num_ranks]):
+            for i, v in enumerate(h):
+                flat[r * n_per + i] = v
+        mask = (_c.c_int32 * self.num_ranks)(*[int(v) for v in active_ranks_mask])
+        _check(_lib.mcep_buffer_sync_nvlink_ipc_handles(self._h, flat, n_per, mask))
+
+    # -- in-process groups / options / diagnostics (no reference counterpart) ---
+    def local_base(self) -> int:
+        p = _c.c_void_p()
+        _check(_lib.mcep_buffer_local_base(self._h, _c.byref(p)))
+        return int(p.value)
+
+    def set_peer_bases(self, bases: List[int], available: Optional[List[int]] = None) -> None:
+        arr = (_c.c_void_p * self.num_ranks)(*bases)
+        av = (_c.c_int32 * self.num_ranks)(*(available or [1] * self.num_ranks))
+        _check(_lib.mcep_buffer_set_peer_bases(self._h, arr, av))
+
+    def set_option(self, name: str, value: int) -> None:
+        _check(_lib.mcep_buffer_set_option(self._h, name.encode(), int(value)))
+
+    def status(self) -> int:
+        out = (_c.c_int32 * 1)()
+        _check(_lib.mcep_buffer_status(self._h, out, 1))
+        return int(out[0])
+
+    # -- the hot path ----------------------------------------------------------
+    def dispatch(self, x_ptr: int, topk_idx_ptr: int, active_ranks_ptr: int, num_tokens: int,
+                 hidden: int, num_topk: int, num_max_dispatch_tokens_per_rank: int,
+                 num_experts: int, timeout_us: int, use_fp8: bool, packed_recv_x_ptr: int,
+                 packed_recv_x_scales_ptr: int, packed_recv_count_ptr: int,
+                 packed_recv_src_info_ptr: int, packed_recv_layout_range_ptr: int,
+                 async_finish: bool, return_recv_hook: bool, compute_stream_ptr: int
+                 ) -> Tuple[Optional[EventHandle], Optional[Callable[[], None]]]:
+        a = self._dargs
+        a.x, a.topk_idx, a.active_ranks = x_ptr, topk_idx_ptr, active_ranks_ptr
+        a.num_tokens, a.hidden, a.num_topk = num_tokens, hidden, num_topk
+        a.num_max_dispatch_tokens_per_rank = num_max_dispatch_tokens_per_rank
+        a.num_experts, a.use_fp8, a.timeout_us = num_experts, int(use_fp8), timeout_us
+        a.packed_recv_x, a.packed_recv_x_scales = packed_recv_x_ptr, packed_recv_x_scales_ptr
+        a.packed_recv_count = packed_recv_count_ptr
+        a.packed_recv_src_info = packed_recv_src_info_ptr
+        a.packed_recv_layout_range = packed_recv_layout_range_ptr
+        a.async_finish, a.return_recv_hook = int(async_finish), int(return_recv_hook)
+        a.compute_stream = compute_stream_ptr
+        ev, hk = _c.c_void_p(), _c.c_void_p()
+        _check(_lib.mcep_dispatch(self._h, _c.byref(a), _c.byref(ev), _c.byref(hk)))
+        return (EventHandle(_adopt=ev.value) if ev.value else None,
+                _Hook(hk.value) if hk.value else None)
+
+    def combine(self, x_ptr: int, topk_idx_ptr: int, topk_weights_ptr: int, src_info_ptr: int,
+                layout_range_ptr: int, active_ranks_ptr: int, num_local_experts: int,
+                num_combined_tokens: int, hidden: int, num_topk: int,
+                num_max_dispatch_tokens_per_rank: int, num_experts: int, timeout_us: int,
+                zero_copy: bool, combined_x_ptr: int, async_finish: bool,
+                return_recv_hook: bool, compute_stream_ptr: int
+                ) -> Tuple[Optional[EventHandle], Optional[Callable[[], None]]]:
+        a = self._cargs
+        a.x, a.topk_idx, a.topk_weights = x_ptr, topk_idx_ptr, topk_weights_ptr
+        a.src_info, a.layout_range, a.active_ranks = src_info_ptr, layout_range_ptr, active_ranks_ptr
+        a.num_local_experts, a.num_combined_tokens = num_local_experts, num_combined_tokens
+        a.hidden, a.num_topk = hidden, num_topk
+        a.num_max_dispatch_tokens_per_rank = num_max_dispatch_tokens_per_rank
+        a.num_experts, a.timeout_us, a.zero_copy = num_experts, timeout_us, int(zero_copy)
+        a.combined_x = combined_x_ptr
+        a.async_finish, a.return_recv_hook = int(async_finish), int(return_recv_hook)
+        a.compute_stream = compute_stream_ptr
+        ev, hk = _c.c_void_p(), _c.c_void_p()
+        _check(_lib.mcep_combine(self._h, _c.byref(a), _c.byref(ev), _c.byref(hk)))
+        return (EventHandle(_adopt=ev.value) if ev.value else None,
+                _Hook(hk.value) if hk.value else None)
+
+
+def routing_layout(topk_idx_ptr: int, num_tokens: int, num_topk: int, num_experts: int,
+                   num_ranks: int, count_ptr: int, rank_count_ptr: int, expert_prefix_ptr: int,
+                   slot_ptr: int, scratch_ptr: int, stream_ptr: int = 0) -> None:
+    """The routing-layout kernel on its own (include/mcep.h: mcep_routing_layout)."""
+    _check(_lib.mcep_routing_layout(topk_idx_ptr, num_tokens, num_topk, num_experts, num_ranks,
+                                    count_ptr, rank_count_ptr, expert_prefix_ptr, slot_ptr,
+                                    scratch_ptr, stream_ptr))
+
+
+def routing_layout_scratch_bytes() -> int:
+    return int(_lib.mcep_routing_layout_scratch_bytes())
