@@ -1,0 +1,117 @@
+"""One rank of a real multi-GPU parity run (one process per GPU, NCCL only for
+the bootstrap). Started by tests/test_gpu_multi.py through torch.distributed.run.
+
+Every rank regenerates all ranks' seeded inputs, runs dispatch + combine through
+the public `Buffer` API concurrently with its peers, and compares its own
+outputs with the CPU oracle. Exit code 0 = parity on this rank."""
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch
+import torch.distributed as dist
+
+from mooncake_b200 import Buffer
+from oracle import ep_oracle as ora
+from tests.ep_harness import make_rank_inputs, mock_expert
+
+
+def run_case(cfg, group, rank, R, buf_cache):
+    M, E, H, K = cfg["M"], cfg["E"], cfg["H"], cfg["K"]
+    L = E // R
+    tokens = cfg.get("tokens") or [cfg["T"]] * R
+    ins = [make_rank_inputs(cfg.get("seed", 1), r, tokens[r], H, E, K,
+                            cfg.get("routing", "uniform"), cfg.get("mask", 0)) for r in range(R)]
+    xs, idxs, ws = [i[0] for i in ins], [i[1] for i in ins], [i[2] for i in ins]
+    active = cfg.get("active") or [1] * R
+    nbytes = Buffer.get_ep_buffer_size_hint(M, H, R, E)
+    key = nbytes
+    if key not in buf_cache:
+        buf_cache.clear()
+        buf_cache[key] = Buffer(group, nbytes)
+    buf = buf_cache[key]
+    if not active[rank]:
+        return  # an inactive rank makes no call
+    x, idx, w = xs[rank].cuda(), idxs[rank].cuda(), ws[rank].cuda()
+    ar = torch.tensor(active, dtype=torch.int32, device="cuda")
+    want = ora.dispatch(xs, idxs, M, E, cfg["fp8"], active=active)[rank]
+    for rep in range(cfg.get("reps", 2)):  # twice: flags, counters and parities are reused
+        mode = cfg.get("mode", "sync")
+        recv, cnt, handle, ev, hook = buf.dispatch(
+            x, idx, ar, M, E, cfg.get("timeout_us", 5_000_000), use_fp8=cfg["fp8"],
+            async_finish=(mode == "async"), return_recv_hook=(mode == "hook"))
+        if hook:
+            hook()
+        if mode == "async":
+            ev.current_stream_wait()
+        torch.cuda.synchronize()
+        rx = recv[0].view(torch.uint8) if cfg["fp8"] else recv
+        assert torch.equal(cnt.cpu(), want["recv_count"]), "recv_count"
+        assert torch.equal(handle[1].cpu(), want["layout_range"]), "layout_range"
+        for le in range(L):
+            n = int(cnt[le])
+            assert torch.equal(handle[0][le, :n].cpu(), want["src_info"][le, :n]), "src_info"
+            assert torch.equal(rx[le, :n].cpu().view(torch.uint8),
+                               want["recv_x"][le, :n].view(torch.uint8)), "payload"
+            if cfg["fp8"]:
+                assert torch.equal(recv[1][le, :n].cpu().contiguous().view(torch.int32),
+                                   want["scales"][le, :n].contiguous().view(torch.int32)), "scales"
+        if cfg["fp8"]:
+            deq = ora.fp8_dequant(rx.cpu().view(-1, H),
+                                  recv[1].cpu().contiguous().view(-1, H // 128)).view(L, -1, H).cuda()
+        else:
+            deq = recv
+        y = mock_expert(torch.nan_to_num(deq.float()).to(torch.bfloat16), rank, L).contiguous()
+        out, ev, hook = buf.combine(y, idx, w, ar, cfg.get("timeout_us", 5_000_000), handle,
+                                    async_finish=(mode == "async"),
+                                    return_recv_hook=(mode == "hook"))
+        if hook:
+            hook()
+        if mode == "async":
+            ev.current_stream_wait()
+        torch.cuda.synchronize()
+        assert ar.cpu().tolist() == active, f"active_ranks changed: {ar.cpu().tolist()}"
+        # closed form: expert e multiplies by (1 + e/16); inactive owners contribute nothing
+        f = 1.0 + idxs[rank].clamp_min(0).float() / 16.0
+        keep = (idxs[rank] >= 0)
+        for r2 in range(R):
+            if not active[r2]:
+                keep &= (idxs[rank] // L) != r2
+        src = xs[rank]
+        if cfg["fp8"]:
+            q, s = ora.fp8_quant(src)
+            src = ora.fp8_dequant(q, s)
+        ref = src.float() * (ws[rank] * f * keep).sum(dim=1, keepdim=True)
+        if ref.numel():
+            err = float((out.cpu().float() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+            assert err < 2e-2, f"combine rel err {err}"
+        assert buf.runtime.status() == 0, "device status word set"
+
+
+def main():
+    cases = json.loads(os.environ["MCEP_TEST_CASES"])
+    rank, R = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    group = dist.group.WORLD
+    cache = {}
+    for name, cfg in cases.items():
+        try:
+            run_case(cfg, group, rank, R, cache)
+        except AssertionError as exc:
+            print(f"[rank {rank}] case {name} FAILED: {exc}", flush=True)
+            raise
+        # ranks leave a case together, on the host, with nothing in flight
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            print(f"case {name} ok", flush=True)
+    cache.clear()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

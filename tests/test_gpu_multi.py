@@ -1,0 +1,46 @@
+"""Real multi-GPU parity: one process per GPU, peers mapped through CUDA IPC,
+ranks running concurrently. Skipped when fewer GPUs are visible."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _cases(R):
+    c = {
+        "c1_bf16": dict(T=128, M=128, H=2048, E=16, K=4, fp8=False, routing="softmax"),
+        "decode_fp8": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True),
+        "decode_fp8_async": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, mode="async", seed=2),
+        "decode_fp8_hook": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, mode="hook", seed=3),
+        "zipf_fp8": dict(T=256, M=256, H=4096, E=128, K=8, fp8=True, routing="zipf1.2"),
+        "mixtral_t1": dict(T=1, M=4, H=4096, E=8, K=2, fp8=False),
+        "mixtral_t1024": dict(T=1024, M=1024, H=4096, E=8, K=2, fp8=False),
+        "ragged": dict(tokens=[(7 * r) % 50 for r in range(R)], M=64, H=640, E=8 * R, K=3,
+                       fp8=True, mask=6),
+    }
+    if R >= 2:
+        # the last rank is marked inactive on every rank and makes no call
+        c["masked_last_rank"] = dict(T=64, M=64, H=4096, E=8, K=2, fp8=False,
+                                     active=[1] * (R - 1) + [0])
+    return c
+
+
+@pytest.mark.parametrize("R", [2, 4, 8])
+def test_multi_gpu_parity(R):
+    if torch.cuda.device_count() < R:
+        pytest.skip(f"needs {R} GPUs")
+    env = dict(os.environ)
+    env["MCEP_TEST_CASES"] = json.dumps(_cases(R))
+    env["NCCL_NVLS_ENABLE"] = "0"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={R}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29620 + R),
+           os.path.join(ROOT, "tests", "mp_worker.py")]
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    tail = (p.stdout + p.stderr)[-4000:]
+    assert p.returncode == 0, tail
