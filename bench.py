@@ -54,6 +54,8 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
     ap.add_argument("--e2e-steps", type=int, default=30)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--force-staged", action="store_true",
+                    help="single rank: go through staging + flags like a multi-rank group")
     ap.add_argument("--inactive-rank", type=int, default=-1,
                     help="mark this rank inactive on every rank; it makes no call")
     return ap.parse_args()
@@ -279,6 +281,8 @@ def run_ours(args):
 
     nbytes = Buffer.get_ep_buffer_size_hint(M, H, R, E)
     buf = Buffer(group, nbytes)
+    if args.force_staged:
+        buf.runtime.set_option("force_staged", 1)
     flush = torch.empty(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
     sync_word = torch.zeros(1, device=dev)
     y = torch.empty((L, R * M, H), dtype=torch.bfloat16, device=dev)

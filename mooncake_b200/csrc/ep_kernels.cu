@@ -73,7 +73,6 @@ std::string drain_kernel_times() {
 namespace kernels {
 
 constexpr int kWarpsPerBlock = 8;
-constexpr int kThreads = kWarpsPerBlock * 32;
 constexpr unsigned kFull = 0xffffffffu;
 
 template <typename... KArgs, typename... Args>
@@ -208,6 +207,7 @@ __global__ void __launch_bounds__(1024)
     for (int i = tid; i < ne * words; i += nthr) mask[i] = 0;
     __syncthreads();
     pdl_wait();
+    pdl_launch_dependents();
     for (int i = tid; i < n; i += nthr) {
         const int e = (int)__ldg(p.topk_idx + i);
         if (e >= e0 && e < e1) {
@@ -216,7 +216,6 @@ __global__ void __launch_bounds__(1024)
         }
     }
     __syncthreads();
-    pdl_launch_dependents();
     for (int le = warp; le < ne; le += nwarps) {
         int carry = 0;
         for (int w0 = 0; w0 < words; w0 += 32) {
@@ -274,103 +273,143 @@ __global__ void __launch_bounds__(1024)
 // =============================================================================
 // dispatch: send
 // =============================================================================
-// Warp item = (token, part of the row). The warp reads its part of the bf16 row
-// once (32 bytes per lane and pass), quantises it in registers when FP8 is on,
-// and stores it to every selected expert's slot: in the staged mode a message
+// One block per token (blocks stride over the tokens), one warp per 512-channel
+// tile of the row. The block reads the bf16 row once (32 bytes per lane),
+// quantises it in registers when FP8 is on, and stores it to every selected
+// expert's slot: in the staged mode a message
 //   [32 B header: token index | payload | 16 B of scales per 512 channels]
-// in the owner rank's receive staging (peer memory over NVLink or local), in the
-// direct mode (single rank) the packed outputs themselves. The warp that
-// completes an expert's last message publishes the (source, expert) flag.
-template <bool kFP8, bool kDirect>
-__global__ void __launch_bounds__(kThreads) ep_dispatch_send_kernel(DispatchSendParams p) {
-    __shared__ char* s_dst[kWarpsPerBlock][kMaxTopk];
-    __shared__ int s_exp[kWarpsPerBlock][kMaxTopk];
-    __shared__ int s_slot[kWarpsPerBlock][kMaxTopk];
+// in the owner rank's receive staging (peer memory over NVLink, or local), in
+// the direct mode (single rank) the packed outputs themselves.
+//
+// kFused: the slots are counted here instead of read from the layout kernel -
+// every block histograms the whole (small) index matrix in shared memory and
+// counts, for its own token, the earlier tokens that chose the same experts.
+// The host uses it when one block per token fits the machine in one wave.
+//
+// Completion: messages are not fenced one by one. A block counts what it sent
+// per expert in shared memory; when its tokens are done it issues ONE
+// system-scope fence, then adds its counts to the per-expert totals. Whoever
+// completes an expert's total publishes the (source, expert) flag.
+__device__ __forceinline__ int topk_entry(const int64_t* topk_idx, int t, int K, int k, int E) {
+    // expert of entry (t, k); -1 when masked, out of range, or a repeat of an
+    // earlier entry of the same token
+    const int e = (int)__ldg(topk_idx + (size_t)t * K + k);
+    if (e < 0 || e >= E) return -1;
+    for (int kk = 0; kk < k; ++kk)
+        if ((int)__ldg(topk_idx + (size_t)t * K + kk) == e) return -1;
+    return e;
+}
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int gwarp = blockIdx.x * kWarpsPerBlock + warp;
-    const int nwarps = gridDim.x * kWarpsPerBlock;
+template <bool kFP8, bool kDirect, bool kFused>
+__global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParams p) {
+    extern __shared__ int smem_i32[];
+    __shared__ char* s_dst[kMaxTopk];
+    __shared__ int s_exp[kMaxTopk];
+    __shared__ int s_slot[kMaxTopk];
+    __shared__ int s_before[kMaxTopk];
+    __shared__ int s_active[kMaxRanks];
+
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int L = p.E / p.R;
     const int RM = p.R * p.M;
     const int nchunks = p.H / 16;
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
     const int S = p.H / 128;
     const char* xb = reinterpret_cast<const char*>(p.x);
+    int* hist = smem_i32;                          // [E] whole-batch counts (fused)
+    int* cta_cnt = smem_i32 + (kFused ? p.E : 0);  // [E] sent by this block (staged)
 
-    pdl_wait();  // slot[] and count[] come from the layout kernel
-
+    pdl_wait();
+    pdl_launch_dependents();
+    if (kFused)
+        for (int e = tid; e < p.E; e += nthr) hist[e] = 0;
     if (!kDirect) {
-        // experts this rank sends nothing to still get their flag
-        for (int e = blockIdx.x * kThreads + threadIdx.x; e < p.E; e += gridDim.x * kThreads) {
-            if (__ldg(p.count + e) == 0) {
-                const int dr = e / L;
-                if (ld_volatile_s32(p.active_ranks + dr)) {
-                    uint64_t* f = reinterpret_cast<uint64_t*>(
-                                      reinterpret_cast<char*>(p.peer_base[dr]) + p.flag_off) +
-                                  ((e - dr * L) * p.R + p.rank);
-                    st_release_sys(f, ((uint64_t)p.seq << 32) | 1u);
+        for (int e = tid; e < p.E; e += nthr) cta_cnt[e] = 0;
+        if (tid < p.R) s_active[tid] = ld_volatile_s32(p.active_ranks + tid);
+    }
+    __syncthreads();
+
+    for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+        const char* xrow = xb + (size_t)t * p.H * 2;
+        // start the row load before the routing work
+        V32 first = {};
+        if (warp < ntiles && warp * 32 + lane < nchunks)
+            first = ld32_readonly(xrow + (size_t)(warp * 32 + lane) * 32);
+        if (tid < kMaxTopk) {
+            s_exp[tid] = tid < p.K ? topk_entry(p.topk_idx, t, p.K, tid, p.E) : -1;
+            s_before[tid] = 0;
+        }
+        __syncthreads();
+        if (kFused && t == (int)blockIdx.x) {
+            // one pass over the index matrix, one token per thread, entries in
+            // registers: whole-batch histogram, and for this block's token the
+            // number of earlier tokens per chosen expert
+            for (int t2 = tid; t2 < p.T; t2 += nthr) {
+                int ev[kMaxTopk];
+#pragma unroll
+                for (int k = 0; k < kMaxTopk; ++k)
+                    ev[k] = k < p.K ? (int)__ldg(p.topk_idx + (size_t)t2 * p.K + k) : -1;
+#pragma unroll
+                for (int k = 0; k < kMaxTopk; ++k) {
+                    int e = ev[k];
+                    if (e >= p.E) e = -1;
+#pragma unroll
+                    for (int kk = 0; kk < k; ++kk)
+                        if (ev[kk] == e) e = -1;
+                    if (e < 0) continue;
+                    atomicAdd(&hist[e], 1);
+                    if (t2 < t)
+                        for (int kk = 0; kk < p.K; ++kk)
+                            if (s_exp[kk] == e) atomicAdd(&s_before[kk], 1);
                 }
             }
+            __syncthreads();
         }
-    }
-
-    const int items = p.T * p.parts;
-    for (int item = gwarp; item < items; item += nwarps) {
-        const int t = item / p.parts, part = item - t * p.parts;
-        char* my_dst = nullptr;
-        int my_e = -1, my_s = -1;
-        if (lane < p.K) {
-            const int e = (int)__ldg(p.topk_idx + t * p.K + lane);
-            const int s = __ldg(p.slot + t * p.K + lane);
-            if (e >= 0 && s >= 0) {
+        if (tid < kMaxTopk) {
+            char* dst = nullptr;
+            int s = -1;
+            const int e = s_exp[tid];
+            if (e >= 0) {
+                s = kFused ? s_before[tid] : __ldg(p.slot + (size_t)t * p.K + tid);
                 if (s >= p.M) {
                     atomicOr(p.status, kStatusSlotRange);
-                } else if (kDirect) {
-                    my_dst = reinterpret_cast<char*>(p.recv_x) +
-                             ((size_t)e * RM + s) * (size_t)p.H * (kFP8 ? 1 : 2);
-                    my_e = e, my_s = s;
-                } else {
-                    const int dr = e / L;
-                    if (ld_volatile_s32(p.active_ranks + dr)) {
-                        my_dst = reinterpret_cast<char*>(p.peer_base[dr]) + p.stage_off +
-                                 ((size_t)((e - dr * L) * p.R + p.rank) * p.M + s) * p.msg_stride;
-                        my_e = e, my_s = s;
+                } else if (s >= 0) {
+                    if (kDirect) {
+                        dst = reinterpret_cast<char*>(p.recv_x) +
+                              ((size_t)e * RM + s) * (size_t)p.H * (kFP8 ? 1 : 2);
+                    } else {
+                        const int dr = e / L;
+                        if (s_active[dr])
+                            dst = reinterpret_cast<char*>(p.peer_base[dr]) + p.stage_off +
+                                  ((size_t)((e - dr * L) * p.R + p.rank) * p.M + s) * p.msg_stride;
                     }
                 }
             }
+            s_dst[tid] = dst;
+            s_slot[tid] = s;
         }
-        if (lane < kMaxTopk) {
-            s_dst[warp][lane] = my_dst;
-            s_exp[warp][lane] = my_e;
-            s_slot[warp][lane] = my_s;
-        }
-        __syncwarp();
+        __syncthreads();
 
-        const int tile0 = part * p.tiles_per_part;
-        const int tile1 = min(ntiles, tile0 + p.tiles_per_part);
-        const char* xrow = xb + (size_t)t * p.H * 2;
-        V32 cur = {};
-        if (tile0 < tile1 && tile0 * 32 + lane < nchunks)
-            cur = ld32_readonly(xrow + (size_t)(tile0 * 32 + lane) * 32);
-        for (int tile = tile0; tile < tile1; ++tile) {
+        for (int tile = warp; tile < ntiles; tile += nwarps) {
             const int c = tile * 32 + lane;
             const bool act = c < nchunks;
-            V32 nxt = {};
-            if (tile + 1 < tile1 && c + 32 < nchunks) nxt = ld32_readonly(xrow + (size_t)(c + 32) * 32);
+            V32 cur = first;
+            if (tile != warp) {
+                cur = V32{};
+                if (act) cur = ld32_readonly(xrow + (size_t)c * 32);
+            }
             if (kFP8) {
                 float sinv;
                 const uint4 q = quantize16(cur, sinv);
                 if (kDirect) {
 #pragma unroll 4
                     for (int k = 0; k < p.K; ++k) {
-                        char* d = s_dst[warp][k];
-                        if (d == nullptr) continue;
-                        if (act) {
-                            st16(d + (size_t)c * 16, q);
-                            if ((lane & 7) == 0)
-                                p.recv_scales[((size_t)s_exp[warp][k] * S + (c >> 3)) * RM +
-                                              s_slot[warp][k]] = sinv;
-                        }
+                        char* d = s_dst[k];
+                        if (d == nullptr || !act) continue;
+                        st16(d + (size_t)c * 16, q);
+                        if ((lane & 7) == 0)
+                            p.recv_scales[((size_t)s_exp[k] * S + (c >> 3)) * RM + s_slot[k]] = sinv;
                     }
                 } else {
                     float4 sc;
@@ -380,7 +419,7 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_send_kernel(DispatchSend
                     sc.w = __shfl_sync(kFull, sinv, 24);
 #pragma unroll 4
                     for (int k = 0; k < p.K; ++k) {
-                        char* d = s_dst[warp][k];
+                        char* d = s_dst[k];
                         if (d == nullptr) continue;
                         if (act) st16(d + kHeaderBytes + (size_t)c * 16, q);
                         if (lane == 0)
@@ -391,34 +430,67 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_send_kernel(DispatchSend
             } else {
 #pragma unroll 4
                 for (int k = 0; k < p.K; ++k) {
-                    char* d = s_dst[warp][k];
-                    if (d == nullptr) continue;
-                    if (act) st32(d + (kDirect ? 0 : kHeaderBytes) + (size_t)c * 32, cur);
+                    char* d = s_dst[k];
+                    if (d == nullptr || !act) continue;
+                    st32(d + (kDirect ? 0 : kHeaderBytes) + (size_t)c * 32, cur);
                 }
             }
-            cur = nxt;
         }
-        if (part == 0 && my_dst != nullptr) {
-            if (kDirect)
-                p.recv_src_info[(size_t)my_e * RM + my_s] = t;
-            else
-                st16(my_dst, make_uint4((uint32_t)t, 0u, 0u, 0u));
-        }
-        __syncwarp();
-        if (!kDirect && my_dst != nullptr) {
-            const int n = __ldg(p.count + my_e);
-            const int old = atom_add_acq_rel_sys(p.done + my_e, 1);
-            if (old + 1 == n * p.parts) {
-                const int dr = my_e / L;
-                uint64_t* f = reinterpret_cast<uint64_t*>(
-                                  reinterpret_cast<char*>(p.peer_base[dr]) + p.flag_off) +
-                              ((my_e - dr * L) * p.R + p.rank);
-                st_release_sys(f, ((uint64_t)p.seq << 32) | (uint32_t)(n + 1));
+        if (tid < p.K && s_dst[tid] != nullptr) {
+            if (kDirect) {
+                p.recv_src_info[(size_t)s_exp[tid] * RM + s_slot[tid]] = t;
+            } else {
+                st16(s_dst[tid], make_uint4((uint32_t)t, 0u, 0u, 0u));
+                atomicAdd(&cta_cnt[s_exp[tid]], 1);
             }
         }
-        __syncwarp();
+        __syncthreads();
     }
-    pdl_launch_dependents();
+
+    // per-expert duties, spread over the grid: the receive layout of a single
+    // rank, or the flag of an expert this rank sends nothing to
+    for (int e = blockIdx.x * nthr + tid; e < p.E; e += gridDim.x * nthr) {
+        const int c = kFused ? hist[e] : __ldg(p.count + e);
+        if (kDirect) {
+            if (kFused) {
+                p.recv_count[e] = c;
+                p.layout_range[e] = c;  // begin 0 | count
+            }
+        } else if (c == 0) {
+            const int dr = e / L;
+            if (s_active[dr]) {
+                uint64_t* f = reinterpret_cast<uint64_t*>(
+                                  reinterpret_cast<char*>(p.peer_base[dr]) + p.flag_off) +
+                              ((e - dr * L) * p.R + p.rank);
+                st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
+            }
+        }
+    }
+    if (!kDirect) {
+        // ONE system-scope fence for everything this block stored (it costs
+        // microseconds even when idle, so it is not paid per message), then the
+        // bookkeeping. Whoever completes an expert's total has, through the
+        // counter, observed every contributor's fence: all of that expert's
+        // messages are performed system-wide, and the flag may follow with only
+        // a device-scope fence in between.
+        if (tid == 0) __threadfence_system();
+        __syncthreads();
+        for (int e = tid; e < p.E; e += nthr) {
+            const int c = cta_cnt[e];
+            if (c == 0) continue;
+            const int total = kFused ? hist[e] : __ldg(p.count + e);
+            const int old = atomicAdd(p.done + e, c);
+            if (old + c == total) {
+                p.done[e] = 0;
+                __threadfence();
+                const int dr = e / L;
+                uint64_t* f = reinterpret_cast<uint64_t*>(
+                                  reinterpret_cast<char*>(p.peer_base[dr]) + p.flag_off) +
+                              ((e - dr * L) * p.R + p.rank);
+                st_relaxed_sys(f, ((uint64_t)p.seq << 32) | (uint32_t)(total + 1));
+            }
+        }
+    }
 }
 
 // =============================================================================
@@ -429,12 +501,13 @@ __global__ void __launch_bounds__(kThreads) ep_dispatch_send_kernel(DispatchSend
 // pack kernel partitions its work by.
 __global__ void __launch_bounds__(1024) ep_dispatch_wait_kernel(DispatchWaitParams p) {
     extern __shared__ int smem_i32[];
-    int* cnt = smem_i32;            // [L*R]
+    int* cnt = smem_i32;              // [L*R]
     int* tot = smem_i32 + p.L * p.R;  // [L + 1]
     __shared__ int s_wt[32];
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int n = p.L * p.R;
     pdl_wait();
+    pdl_launch_dependents();
     for (int i = tid; i < n; i += nthr) {
         const int src = i % p.R;
         const uint32_t v = wait_flag(p.flags + i, p.seq, p.active_ranks, src, p.timeout_ns,
@@ -442,7 +515,6 @@ __global__ void __launch_bounds__(1024) ep_dispatch_wait_kernel(DispatchWaitPara
         cnt[i] = v ? (int)v - 1 : 0;
     }
     __syncthreads();
-    pdl_launch_dependents();
     for (int le = tid; le < p.L; le += nthr) {
         int begin = 0;
         for (int src = 0; src < p.R; ++src) {
@@ -468,151 +540,148 @@ __global__ void __launch_bounds__(1024) ep_dispatch_wait_kernel(DispatchWaitPara
 // =============================================================================
 // dispatch: pack the staged messages into the caller's tensors
 // =============================================================================
+// One block per received row (blocks stride over the rows), one warp per tile.
 template <bool kFP8>
-__global__ void __launch_bounds__(kThreads) ep_dispatch_pack_kernel(DispatchPackParams p) {
+__global__ void __launch_bounds__(512) ep_dispatch_pack_kernel(DispatchPackParams p) {
     extern __shared__ int smem_i32[];
     int* pre = smem_i32;  // [L*R + 1]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int n = p.L * p.R;
     const int RM = p.R * p.M;
     const int nchunks = p.H / 16;
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
     const int S = p.H / 128;
     pdl_wait();
-    for (int i = threadIdx.x; i <= n; i += kThreads) pre[i] = __ldcg(p.pack_prefix + i);
-    __syncthreads();
     pdl_launch_dependents();
+    for (int i = tid; i <= n; i += nthr) pre[i] = __ldcg(p.pack_prefix + i);
+    __syncthreads();
     const int total = pre[n];
-    const long long items = (long long)total * p.parts;
-    for (long long item = (long long)blockIdx.x * kWarpsPerBlock + warp; item < items;
-         item += (long long)gridDim.x * kWarpsPerBlock) {
-        const int g = (int)(item / p.parts), part = (int)(item - (long long)g * p.parts);
+    for (int g = blockIdx.x; g < total; g += gridDim.x) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R;
         const int j = g - pre[i];
         const int row = (int)(__ldcg(p.layout_range + i) >> 32) + j;
         if (j >= p.M || row >= RM) {
-            if (lane == 0) atomicOr(p.status, kStatusSlotRange);
+            if (tid == 0) atomicOr(p.status, kStatusSlotRange);
             continue;
         }
         const char* msg = p.stage + ((size_t)i * p.M + j) * p.msg_stride;
         const size_t out_row = (size_t)le * RM + row;
-        const int tile0 = part * p.tiles_per_part;
-        const int tile1 = min(ntiles, tile0 + p.tiles_per_part);
-        for (int tile = tile0; tile < tile1; ++tile) {
+        for (int tile = warp; tile < ntiles; tile += nwarps) {
             const int c = tile * 32 + lane;
-            if (kFP8) {
-                if (c < nchunks)
-                    st16(reinterpret_cast<char*>(p.recv_x) + out_row * p.H + (size_t)c * 16,
-                         ld16_coherent(msg + kHeaderBytes + (size_t)c * 16));
-                const int gi = tile * 4 + lane;
-                if (lane < 4 && gi < S)
-                    p.recv_scales[((size_t)le * S + gi) * RM + row] =
-                        ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)gi * 4);
-            } else {
-                if (c < nchunks)
-                    st32(reinterpret_cast<char*>(p.recv_x) + (out_row * p.H + (size_t)c * 16) * 2,
-                         ld32_coherent(msg + kHeaderBytes + (size_t)c * 32));
-            }
+            if (c >= nchunks) continue;
+            if (kFP8)
+                st16(reinterpret_cast<char*>(p.recv_x) + out_row * p.H + (size_t)c * 16,
+                     ld16_coherent(msg + kHeaderBytes + (size_t)c * 16));
+            else
+                st32(reinterpret_cast<char*>(p.recv_x) + (out_row * p.H + (size_t)c * 16) * 2,
+                     ld32_coherent(msg + kHeaderBytes + (size_t)c * 32));
         }
-        if (part == 0 && lane == 0) p.recv_src_info[out_row] = ld_s32_coherent(msg);
+        if (kFP8)
+            for (int gi = tid; gi < S; gi += nthr)
+                p.recv_scales[((size_t)le * S + gi) * RM + row] =
+                    ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)gi * 4);
+        if (tid == nthr - 1) p.recv_src_info[out_row] = ld_s32_coherent(msg);
     }
 }
 
 // =============================================================================
 // combine: send expert outputs back to the token owners
 // =============================================================================
-// Warp item = (packed row, part). Row r of local expert le that came from rank
-// d's token t goes to d's combine staging slot [global expert][t]
-// (the slot rule of mooncake-ep/src/mooncake_ep_kernel.cu:633-637). The warp that
-// completes a (expert, destination) segment publishes that expert's flag at d.
-__global__ void __launch_bounds__(kThreads) ep_combine_send_kernel(CombineSendParams p) {
+// One block per packed row, one warp per tile. Row r of local expert le that
+// came from rank d's token t goes to d's combine staging slot [global expert][t]
+// (the slot rule of mooncake-ep/src/mooncake_ep_kernel.cu:633-637). Completion
+// is counted per (expert, destination) segment the same way dispatch counts per
+// expert: one system fence per block, then shared-memory counts are added to the
+// global ones and whoever completes a segment publishes that expert's flag at d.
+__global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams p) {
     extern __shared__ int smem_i32[];
-    int* pre = smem_i32;  // [L*R + 1]
+    int* pre = smem_i32;                     // [L*R + 1]
+    int* cta_cnt = smem_i32 + p.L * p.R + 1;  // [L*R]
     __shared__ int s_wt[32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int n = p.L * p.R;
     const int RM = p.R * p.M;
     const int nchunks = p.H / 16;
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
+    __shared__ int s_active[kMaxRanks];
     pdl_wait();
-    for (int i = threadIdx.x; i < n; i += kThreads)
+    pdl_launch_dependents();
+    for (int i = tid; i < n; i += nthr) {
         pre[i] = (int)(__ldg(p.layout_range + i) & 0xffffffffll);
+        cta_cnt[i] = 0;
+    }
+    if (tid < p.R) s_active[tid] = ld_volatile_s32(p.active_ranks + tid);
     __syncthreads();
     // empty segments: flag right away
-    for (int i = blockIdx.x * kThreads + threadIdx.x; i < n; i += gridDim.x * kThreads) {
+    for (int i = blockIdx.x * nthr + tid; i < n; i += gridDim.x * nthr) {
         if (pre[i] == 0) {
             const int d = i % p.R, le = i / p.R;
-            if (ld_volatile_s32(p.active_ranks + d)) {
+            if (s_active[d]) {
                 uint64_t* f = reinterpret_cast<uint64_t*>(
                                   reinterpret_cast<char*>(p.peer_base[d]) + p.flag_off) +
                               (p.rank * p.L + le);
-                st_release_sys(f, ((uint64_t)p.seq << 32) | 1u);
+                st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
             }
         }
     }
     __syncthreads();
     block_exclusive_scan(pre, n, s_wt);
     const int total = pre[n];
-    const long long items = (long long)total * p.parts;
     const char* xb = reinterpret_cast<const char*>(p.x);
-    for (long long item = (long long)blockIdx.x * kWarpsPerBlock + warp; item < items;
-         item += (long long)gridDim.x * kWarpsPerBlock) {
-        const int g = (int)(item / p.parts), part = (int)(item - (long long)g * p.parts);
+    for (int g = blockIdx.x; g < total; g += gridDim.x) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R, d = i - le * p.R;
         const int j = g - pre[i];
-        const long long lr = __ldg(p.layout_range + i);
-        const int cnt = (int)(lr & 0xffffffffll);
-        const int row = (int)(lr >> 32) + j;
-        const bool live = ld_volatile_s32(p.active_ranks + d) != 0;
+        const int row = (int)(__ldg(p.layout_range + i) >> 32) + j;
+        const bool live = s_active[d] != 0;
         int t = -1;
         if (row < RM) t = __ldg(p.src_info + (size_t)le * RM + row);
         if (t < 0 || t >= p.M) {
-            if (lane == 0) atomicOr(p.status, kStatusBadSource);
+            if (tid == 0) atomicOr(p.status, kStatusBadSource);
         } else if (live) {
             const char* src = xb + ((size_t)le * RM + row) * p.H * 2;
             char* dst = reinterpret_cast<char*>(p.peer_base[d]) + p.stage_off +
                         ((size_t)(p.rank * p.L + le) * p.M + t) * p.H * 2;
-            const int tile0 = part * p.tiles_per_part;
-            const int tile1 = min(ntiles, tile0 + p.tiles_per_part);
-            V32 cur = {};
-            if (tile0 < tile1 && tile0 * 32 + lane < nchunks)
-                cur = ld32_readonly(src + (size_t)(tile0 * 32 + lane) * 32);
-            for (int tile = tile0; tile < tile1; ++tile) {
+            for (int tile = warp; tile < ntiles; tile += nwarps) {
                 const int c = tile * 32 + lane;
-                V32 nxt = {};
-                if (tile + 1 < tile1 && c + 32 < nchunks)
-                    nxt = ld32_readonly(src + (size_t)(c + 32) * 32);
-                if (c < nchunks) st32(dst + (size_t)c * 32, cur);
-                cur = nxt;
+                if (c < nchunks) st32(dst + (size_t)c * 32, ld32_readonly(src + (size_t)c * 32));
             }
         }
-        __syncwarp();
-        if (lane == 0) {
-            const int old = atom_add_acq_rel_sys(p.done + i, 1);
-            if (old + 1 == cnt * p.parts) {
-                p.done[i] = 0;
-                if (live) {
-                    uint64_t* f = reinterpret_cast<uint64_t*>(
-                                      reinterpret_cast<char*>(p.peer_base[d]) + p.flag_off) +
-                                  (p.rank * p.L + le);
-                    st_release_sys(f, ((uint64_t)p.seq << 32) | 1u);
-                }
+        if (tid == 0) cta_cnt[i] += 1;
+    }
+    __syncthreads();
+    if (tid == 0) __threadfence_system();
+    __syncthreads();
+    for (int i = tid; i < n; i += nthr) {
+        const int c = cta_cnt[i];
+        if (c == 0) continue;
+        const int cnt = (int)(__ldg(p.layout_range + i) & 0xffffffffll);
+        const int old = atomicAdd(p.done + i, c);
+        if (old + c == cnt) {
+            p.done[i] = 0;
+            const int d = i % p.R, le = i / p.R;
+            if (s_active[d]) {
+                __threadfence();  // see the dispatch send kernel: one system fence per block
+                uint64_t* f = reinterpret_cast<uint64_t*>(
+                                  reinterpret_cast<char*>(p.peer_base[d]) + p.flag_off) +
+                              (p.rank * p.L + le);
+                st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
             }
         }
     }
-    pdl_launch_dependents();
 }
 
 // One block; thread e waits for expert e's flag
 // (mooncake-ep/src/mooncake_ep_kernel.cu:685-699).
 __global__ void __launch_bounds__(1024) ep_combine_wait_kernel(CombineWaitParams p) {
     pdl_wait();
+    pdl_launch_dependents();
     for (int e = threadIdx.x; e < p.E; e += blockDim.x)
         (void)wait_flag(p.flags + e, p.seq, p.active_ranks, e / p.L, p.timeout_ns,
                         p.hard_timeout_ns, p.status);
-    pdl_launch_dependents();
 }
 
 // Single rank: rowmap[t][k] = packed row of (token t, expert topk[t][k]) as the
@@ -621,6 +690,7 @@ __global__ void __launch_bounds__(256) ep_combine_invert_kernel(CombineInvertPar
     const int RM = p.R * p.M;
     const long long total = (long long)p.L * p.M;
     pdl_wait();
+    pdl_launch_dependents();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int le = (int)(i / p.M), j = (int)(i - (long long)le * p.M);
@@ -641,59 +711,62 @@ __global__ void __launch_bounds__(256) ep_combine_invert_kernel(CombineInvertPar
         for (int k = 0; k < p.K; ++k)
             if ((int)__ldg(p.topk_idx + (size_t)t * p.K + k) == e) p.rowmap[(size_t)t * p.K + k] = row;
     }
-    pdl_launch_dependents();
 }
 
 // =============================================================================
 // combine: weighted top-k reduction
 // =============================================================================
-// Warp item = (token, 512-channel tile); each lane owns 16 channels: up to K
-// 32-byte loads in flight, fp32 FMA accumulation in k order, one bf16 rounding,
-// one 32-byte store (the arithmetic of mooncake_ep_kernel.cu:715-752).
+// One block per token, one warp per 512-channel tile; each lane owns 16
+// channels: up to K 32-byte loads in flight, fp32 FMA accumulation in k order,
+// one bf16 rounding, one 32-byte store (mooncake_ep_kernel.cu:715-752).
 template <bool kDirect>
-__global__ void __launch_bounds__(kThreads) ep_combine_reduce_kernel(CombineReduceParams p) {
-    __shared__ const char* s_ptr[kWarpsPerBlock][kMaxTopk];
-    __shared__ float s_w[kWarpsPerBlock][kMaxTopk];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReduceParams p) {
+    __shared__ const char* s_ptr[kMaxTopk];
+    __shared__ float s_w[kMaxTopk];
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int nchunks = p.H / 16;
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
-    const long long items = (long long)p.T * ntiles;
+    __shared__ int s_active[kMaxRanks];
     pdl_wait();
-    for (long long item = (long long)blockIdx.x * kWarpsPerBlock + warp; item < items;
-         item += (long long)gridDim.x * kWarpsPerBlock) {
-        const int t = (int)(item / ntiles), tile = (int)(item - (long long)t * ntiles);
-        const char* ptr = nullptr;
-        float w = 0.f;
-        if (lane < p.K) {
-            const int e = (int)__ldg(p.topk_idx + (size_t)t * p.K + lane);
-            w = __ldg(p.topk_weights + (size_t)t * p.K + lane);
-            if (e >= 0 && e < p.E && ld_volatile_s32(p.active_ranks + e / p.L)) {
-                if (kDirect) {
-                    const int r = __ldcg(p.rowmap + (size_t)t * p.K + lane);
-                    if (r >= 0 && r < p.RM)
-                        ptr = reinterpret_cast<const char*>(p.x) + ((size_t)e * p.RM + r) * p.H * 2;
-                } else {
-                    ptr = p.stage + ((size_t)e * p.M + t) * p.H * 2;
+    pdl_launch_dependents();
+    if (tid < p.E / p.L) s_active[tid] = ld_volatile_s32(p.active_ranks + tid);
+    __syncthreads();
+    for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+        if (tid < kMaxTopk) {
+            const char* ptr = nullptr;
+            float w = 0.f;
+            if (tid < p.K) {
+                // independent loads first, so they overlap
+                const int e = (int)__ldg(p.topk_idx + (size_t)t * p.K + tid);
+                w = __ldg(p.topk_weights + (size_t)t * p.K + tid);
+                const int r = kDirect ? __ldcg(p.rowmap + (size_t)t * p.K + tid) : 0;
+                if (e >= 0 && e < p.E && s_active[e / p.L]) {
+                    if (kDirect) {
+                        if (r >= 0 && r < p.RM)
+                            ptr = reinterpret_cast<const char*>(p.x) + ((size_t)e * p.RM + r) * p.H * 2;
+                    } else {
+                        ptr = p.stage + ((size_t)e * p.M + t) * p.H * 2;
+                    }
                 }
             }
+            s_ptr[tid] = ptr;
+            s_w[tid] = w;
         }
-        if (lane < kMaxTopk) {
-            s_ptr[warp][lane] = ptr;
-            s_w[warp][lane] = w;
-        }
-        __syncwarp();
-        const int c = tile * 32 + lane;
-        if (c < nchunks) {
+        __syncthreads();
+        for (int tile = warp; tile < ntiles; tile += nwarps) {
+            const int c = tile * 32 + lane;
+            if (c >= nchunks) continue;
             float acc[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) acc[i] = 0.f;
 #pragma unroll 4
             for (int k = 0; k < p.K; ++k) {
-                const char* rp = s_ptr[warp][k];
+                const char* rp = s_ptr[k];
                 if (rp == nullptr) continue;
                 const V32 v = kDirect ? ld32_readonly(rp + (size_t)c * 32)
                                       : ld32_coherent(rp + (size_t)c * 32);
-                const float wk = s_w[warp][k];
+                const float wk = s_w[k];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     acc[2 * i] = fmaf(bf16lo(v.w[i]), wk, acc[2 * i]);
@@ -703,16 +776,25 @@ __global__ void __launch_bounds__(kThreads) ep_combine_reduce_kernel(CombineRedu
             st32(reinterpret_cast<char*>(p.combined_x) + ((size_t)t * p.H + (size_t)c * 16) * 2,
                  pack_bf16x16(acc));
         }
-        __syncwarp();
+        __syncthreads();
     }
 }
 
-inline int grid_for_warp_items(long long items, const LaunchCtx& ctx, int blocks_per_sm) {
-    long long blocks = (items + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    long long cap = (long long)ctx.num_sms * blocks_per_sm;
-    if (blocks > cap) blocks = cap;
-    if (blocks < 1) blocks = 1;
-    return (int)blocks;
+// threads per block: one warp per tile, at most 16 warps
+inline int block_threads(int H) {
+    int ntiles = (H + kTileChannels - 1) / kTileChannels;
+    if (ntiles > 16) ntiles = 16;
+    if (ntiles < 1) ntiles = 1;
+    return ntiles * 32;
+}
+// a grid that fills the machine once (blocks stride over the work items)
+inline int persistent_grid(long long items, int threads, const LaunchCtx& ctx) {
+    int per_sm = 2048 / threads;
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 16) per_sm = 16;
+    long long cap = (long long)ctx.num_sms * per_sm;
+    long long g = items < cap ? items : cap;
+    return (int)(g < 1 ? 1 : g);
 }
 
 }  // namespace kernels
@@ -723,8 +805,13 @@ using namespace kernels;
 // =============================================================================
 cudaError_t launch_layout(const LayoutParams& p, const LaunchCtx& ctx) {
     const int words = (p.T + 31) / 32 > 0 ? (p.T + 31) / 32 : 1;
-    // experts per block: spread over the SMs, bounded by shared memory
-    int epc = (p.E + ctx.num_sms - 1) / ctx.num_sms;
+    const long long n = (long long)p.T * p.K;
+    // Every block reads the whole index matrix, so the number of blocks trades
+    // parallelism against L2 traffic: keep blocks * n * 8 bytes around 8 MB.
+    long long max_blocks = n > 0 ? (1ll << 20) / n : ctx.num_sms;
+    if (max_blocks < 8) max_blocks = 8;
+    if (max_blocks > ctx.num_sms) max_blocks = ctx.num_sms;
+    int epc = (int)((p.E + max_blocks - 1) / max_blocks);
     if (epc < 1) epc = 1;
     const size_t budget = 200 * 1024;
     while (epc > 1 && (size_t)epc * words * 8 > budget) --epc;
@@ -736,24 +823,40 @@ cudaError_t launch_layout(const LayoutParams& p, const LaunchCtx& ctx) {
                                              (int)smem);
         if (e != cudaSuccess) return e;
     }
-    const int n = p.T * p.K;
     int threads = 128;
     while (threads < 1024 && threads * 4 < n) threads <<= 1;
     const int grid = (p.E + epc - 1) / epc;
-    return launch("ep_routing_layout", ep_routing_layout_kernel, dim3(grid), dim3(threads), smem, ctx, p, epc, words);
+    return launch("ep_routing_layout", ep_routing_layout_kernel, dim3(grid), dim3(threads), smem,
+                  ctx, p, epc, words);
+}
+
+bool dispatch_send_can_fuse_layout(int T, int K, int H, int num_sms) {
+    // one block per token in a single wave, and an index matrix small enough to
+    // be scanned by every block
+    const int threads = block_threads(H);
+    int per_sm = 2048 / threads;
+    if (per_sm > 16) per_sm = 16;
+    return (long long)T * K <= 4096 && T <= num_sms * per_sm;
 }
 
 cudaError_t launch_dispatch_send(const DispatchSendParams& p, const LaunchCtx& ctx) {
-    const long long items = (long long)p.T * p.parts;
-    int grid = grid_for_warp_items(items, ctx, 8);
-    // enough threads to cover the zero-count flag loop in one pass when cheap
-    const int min_grid = (p.E + kThreads - 1) / kThreads;
-    if (!p.direct && grid < min_grid) grid = min_grid;
-    auto k = p.use_fp8 ? (p.direct ? ep_dispatch_send_kernel<true, true>
-                                   : ep_dispatch_send_kernel<true, false>)
-                       : (p.direct ? ep_dispatch_send_kernel<false, true>
-                                   : ep_dispatch_send_kernel<false, false>);
-    return launch(p.direct ? "ep_dispatch_send_direct" : "ep_dispatch_send", k, dim3(grid), dim3(kThreads), 0, ctx, p);
+    const int threads = block_threads(p.H);
+    int grid = p.fused ? (p.T > 0 ? p.T : 1) : persistent_grid(p.T, threads, ctx);
+    const size_t smem = (size_t)((p.fused ? p.E : 0) + (p.direct ? 0 : p.E)) * sizeof(int);
+    void (*k)(DispatchSendParams) = nullptr;
+    const int sel = (p.use_fp8 ? 4 : 0) | (p.direct ? 2 : 0) | (p.fused ? 1 : 0);
+    switch (sel) {
+        case 0: k = ep_dispatch_send_kernel<false, false, false>; break;
+        case 1: k = ep_dispatch_send_kernel<false, false, true>; break;
+        case 2: k = ep_dispatch_send_kernel<false, true, false>; break;
+        case 3: k = ep_dispatch_send_kernel<false, true, true>; break;
+        case 4: k = ep_dispatch_send_kernel<true, false, false>; break;
+        case 5: k = ep_dispatch_send_kernel<true, false, true>; break;
+        case 6: k = ep_dispatch_send_kernel<true, true, false>; break;
+        default: k = ep_dispatch_send_kernel<true, true, true>; break;
+    }
+    return launch(p.direct ? "ep_dispatch_send_direct" : "ep_dispatch_send", k, dim3(grid),
+                  dim3(threads), smem, ctx, p);
 }
 
 cudaError_t launch_dispatch_wait(const DispatchWaitParams& p, const LaunchCtx& ctx) {
@@ -765,20 +868,19 @@ cudaError_t launch_dispatch_wait(const DispatchWaitParams& p, const LaunchCtx& c
 }
 
 cudaError_t launch_dispatch_pack(const DispatchPackParams& p, const LaunchCtx& ctx) {
-    // the row count is only known on the device: size for the worst case the
-    // machine can hold at once and let the blocks stride
-    const long long worst = (long long)p.L * p.R * p.M * p.parts;
-    const int grid = grid_for_warp_items(worst, ctx, 8);
+    // the row count is only known on the device: one wave of blocks that stride
+    const int threads = block_threads(p.H);
+    const int grid = persistent_grid((long long)p.L * p.R * p.M, threads, ctx);
     const size_t smem = (size_t)(p.L * p.R + 1) * sizeof(int);
     auto k = p.use_fp8 ? ep_dispatch_pack_kernel<true> : ep_dispatch_pack_kernel<false>;
-    return launch("ep_dispatch_pack", k, dim3(grid), dim3(kThreads), smem, ctx, p);
+    return launch("ep_dispatch_pack", k, dim3(grid), dim3(threads), smem, ctx, p);
 }
 
 cudaError_t launch_combine_send(const CombineSendParams& p, const LaunchCtx& ctx) {
-    const long long worst = (long long)p.L * p.R * p.M * p.parts;
-    int grid = grid_for_warp_items(worst, ctx, 8);
-    const size_t smem = (size_t)(p.L * p.R + 1) * sizeof(int);
-    return launch("ep_combine_send", ep_combine_send_kernel, dim3(grid), dim3(kThreads), smem, ctx, p);
+    const int threads = block_threads(p.H);
+    const int grid = persistent_grid((long long)p.L * p.R * p.M, threads, ctx);
+    const size_t smem = (size_t)(2 * p.L * p.R + 1) * sizeof(int);
+    return launch("ep_combine_send", ep_combine_send_kernel, dim3(grid), dim3(threads), smem, ctx, p);
 }
 
 cudaError_t launch_combine_wait(const CombineWaitParams& p, const LaunchCtx& ctx) {
@@ -793,14 +895,16 @@ cudaError_t launch_combine_invert(const CombineInvertParams& p, const LaunchCtx&
     const long long cap = (long long)ctx.num_sms * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    return launch("ep_combine_invert", ep_combine_invert_kernel, dim3((int)blocks), dim3(256), 0, ctx, p);
+    return launch("ep_combine_invert", ep_combine_invert_kernel, dim3((int)blocks), dim3(256), 0,
+                  ctx, p);
 }
 
 cudaError_t launch_combine_reduce(const CombineReduceParams& p, const LaunchCtx& ctx) {
-    const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
-    const int grid = grid_for_warp_items((long long)p.T * ntiles, ctx, 8);
+    const int threads = block_threads(p.H);
+    const int grid = persistent_grid(p.T, threads, ctx);
     auto k = p.direct ? ep_combine_reduce_kernel<true> : ep_combine_reduce_kernel<false>;
-    return launch(p.direct ? "ep_combine_reduce_direct" : "ep_combine_reduce", k, dim3(grid), dim3(kThreads), 0, ctx, p);
+    return launch(p.direct ? "ep_combine_reduce_direct" : "ep_combine_reduce", k, dim3(grid),
+                  dim3(threads), 0, ctx, p);
 }
 
 }  // namespace mcep

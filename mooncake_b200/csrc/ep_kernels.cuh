@@ -11,6 +11,7 @@
 namespace mcep {
 
 constexpr int kMaxTopk = 16;       // MCEP_MAX_TOPK
+constexpr int kMaxRanks = 64;      // ranks of one group (one NVLink domain)
 constexpr int kTileChannels = 512; // one warp pass: 32 lanes x 16 channels
 constexpr int kHeaderBytes = 32;   // staged message header (token index + padding)
 
@@ -52,7 +53,7 @@ struct DispatchSendParams {
     void* const* peer_base;     // [R] base of every rank's symmetric buffer
     int T, K, E, R, M, H, rank;
     int use_fp8;
-    int parts, tiles_per_part;  // a token row is split into `parts` warp items
+    int fused;                  // count the slots here (slot/count unused) - small batches
     size_t stage_off;           // dispatch staging of this call's parity
     size_t flag_off;            // dispatch flags of this call's parity
     size_t msg_stride;
@@ -63,7 +64,11 @@ struct DispatchSendParams {
     void* recv_x;
     float* recv_scales;
     int32_t* recv_src_info;
+    int32_t* recv_count;        // direct + fused: [E]
+    int64_t* layout_range;      // direct + fused: [E]
 };
+// whether the send kernel may count the slots itself for this problem size
+bool dispatch_send_can_fuse_layout(int T, int K, int H, int num_sms);
 cudaError_t launch_dispatch_send(const DispatchSendParams& p, const LaunchCtx& ctx);
 
 struct DispatchWaitParams {
@@ -86,7 +91,6 @@ struct DispatchPackParams {
     const int64_t* layout_range;
     int L, R, M, H;
     int use_fp8;
-    int parts, tiles_per_part;
     size_t msg_stride;
     void* recv_x;
     float* recv_scales;
@@ -104,7 +108,6 @@ struct CombineSendParams {
     void* const* peer_base;
     int32_t* done;              // [L*R] completion counters (zero on entry, zero on exit)
     int L, R, M, H, rank;
-    int parts, tiles_per_part;
     size_t stage_off;           // combine staging of this parity
     size_t flag_off;            // combine flags of this parity
     uint32_t seq;

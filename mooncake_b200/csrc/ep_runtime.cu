@@ -72,6 +72,7 @@ struct mcep_buffer {
     bool all_peers = false;
     bool force_staged = false;
     bool pdl = true;
+    bool fuse_layout = true;
     int64_t hard_timeout_ns = 10ll * 1000 * 1000 * 1000;
     char* base = nullptr;            // symmetric allocation: header region + data area
     char* workspace = nullptr;
@@ -114,17 +115,6 @@ Geometry geometry(int R, int E, int M, int H, bool fp8) {
     g.cstage_bytes = (size_t)E * M * 2 * (size_t)H;
     g.parity_bytes = g.dstage_bytes + g.cstage_bytes;
     return g;
-}
-
-// Split a row into enough warp items to fill the machine when tokens are few.
-void choose_parts(int rows, int ntiles, int num_sms, int* parts, int* tiles_per_part) {
-    const long long want = (long long)num_sms * 16;  // warps in flight we aim for
-    long long p = rows > 0 ? (want + rows - 1) / rows : 1;
-    if (p < 1) p = 1;
-    if (p > ntiles) p = ntiles;
-    int tpp = (int)((ntiles + p - 1) / p);
-    *tiles_per_part = tpp;
-    *parts = (ntiles + tpp - 1) / tpp;
 }
 
 int64_t to_ns(int64_t timeout_us) { return timeout_us < 0 ? -1 : timeout_us * 1000; }
@@ -178,7 +168,7 @@ uint64_t mcep_get_ep_buffer_size_hint(int M, int hidden, int num_ranks, int num_
 int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int disable_p2p,
                        mcep_buffer** out) {
     MCEP_REQUIRE(out != nullptr);
-    MCEP_REQUIRE(num_ranks >= 1 && rank >= 0 && rank < num_ranks);
+    MCEP_REQUIRE(num_ranks >= 1 && num_ranks <= mcep::kMaxRanks && rank >= 0 && rank < num_ranks);
     MCEP_REQUIRE(num_ep_buffer_bytes >= 0);
     auto* b = new mcep_buffer();
     b->rank = rank;
@@ -344,6 +334,8 @@ int mcep_buffer_set_option(mcep_buffer* b, const char* name, int64_t value) {
         b->hard_timeout_ns = value * 1000 * 1000;
     } else if (!std::strcmp(name, "pdl")) {
         b->pdl = value != 0;
+    } else if (!std::strcmp(name, "fuse_layout")) {
+        b->fuse_layout = value != 0;
     } else {
         return fail(MCEP_ERR_INVALID, "Failed: unknown option '%s'", name);
     }
@@ -410,29 +402,30 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     mcep::LaunchCtx first{stream, b->num_sms, false};
     mcep::LaunchCtx next{stream, b->num_sms, b->pdl};
 
-    int parts = 1, tpp = g.ntiles;
-    choose_parts(T, g.ntiles, b->num_sms, &parts, &tpp);
-
-    mcep::LayoutParams lp = {};
-    lp.topk_idx = a->topk_idx;
-    lp.T = T, lp.K = K, lp.E = E, lp.R = R;
-    lp.count = sc.count, lp.slot = sc.slot, lp.done = sc.done, lp.ticket = sc.ticket;
-    if (direct) {
-        lp.recv_count = a->packed_recv_count;
-        lp.layout_range = a->packed_recv_layout_range;
+    const bool fused = mcep::dispatch_send_can_fuse_layout(T, K, H, b->num_sms) && b->fuse_layout;
+    if (!fused) {
+        mcep::LayoutParams lp = {};
+        lp.topk_idx = a->topk_idx;
+        lp.T = T, lp.K = K, lp.E = E, lp.R = R;
+        lp.count = sc.count, lp.slot = sc.slot, lp.done = sc.done, lp.ticket = sc.ticket;
+        if (direct) {
+            lp.recv_count = a->packed_recv_count;
+            lp.layout_range = a->packed_recv_layout_range;
+        }
+        MCEP_CUDA(mcep::launch_layout(lp, first));
     }
-    MCEP_CUDA(mcep::launch_layout(lp, first));
 
     mcep::DispatchSendParams sp = {};
     sp.x = a->x, sp.topk_idx = a->topk_idx, sp.slot = sc.slot, sp.count = sc.count;
     sp.done = sc.done, sp.active_ranks = a->active_ranks, sp.peer_base = b->peer_dev;
     sp.T = T, sp.K = K, sp.E = E, sp.R = R, sp.M = M, sp.H = H, sp.rank = b->rank;
-    sp.use_fp8 = fp8, sp.parts = parts, sp.tiles_per_part = tpp;
+    sp.use_fp8 = fp8, sp.fused = fused;
     sp.stage_off = data0, sp.flag_off = dflag_off, sp.msg_stride = g.msg_stride;
     sp.seq = seq, sp.status = b->status;
     sp.direct = direct, sp.recv_x = a->packed_recv_x, sp.recv_scales = a->packed_recv_x_scales;
     sp.recv_src_info = a->packed_recv_src_info;
-    MCEP_CUDA(mcep::launch_dispatch_send(sp, next));
+    sp.recv_count = a->packed_recv_count, sp.layout_range = a->packed_recv_layout_range;
+    MCEP_CUDA(mcep::launch_dispatch_send(sp, fused ? first : next));
 
     // receive phase, now or from the hook
     mcep::DispatchWaitParams wp = {};
@@ -446,8 +439,6 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     pp.stage = b->base + data0, pp.pack_prefix = sc.pack_prefix;
     pp.layout_range = a->packed_recv_layout_range;
     pp.L = g.L, pp.R = R, pp.M = M, pp.H = H, pp.use_fp8 = fp8;
-    // rows per rank are not known on the host; size the split for an even spread
-    choose_parts((int)((long long)T * K), g.ntiles, b->num_sms, &pp.parts, &pp.tiles_per_part);
     pp.msg_stride = g.msg_stride, pp.recv_x = a->packed_recv_x;
     pp.recv_scales = a->packed_recv_x_scales, pp.recv_src_info = a->packed_recv_src_info;
     pp.status = b->status;
@@ -542,7 +533,6 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
         sp.x = a->x, sp.src_info = a->src_info, sp.layout_range = a->layout_range;
         sp.active_ranks = a->active_ranks, sp.peer_base = b->peer_dev, sp.done = sc.cdone;
         sp.L = g.L, sp.R = R, sp.M = M, sp.H = H, sp.rank = b->rank;
-        choose_parts((int)((long long)T * K), g.ntiles, b->num_sms, &sp.parts, &sp.tiles_per_part);
         sp.stage_off = cstage_off, sp.flag_off = cflag_off, sp.seq = seq, sp.status = b->status;
         MCEP_CUDA(mcep::launch_combine_send(sp, first));
     }

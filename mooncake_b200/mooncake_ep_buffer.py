@@ -73,9 +73,10 @@ class Buffer:
             raise RuntimeError("Mooncake EP (B200): P2P disabled and no RDMA route exists; "
                                "there is no fallback path")
         mine = self.runtime.get_ipc_handle()
-        device = torch.device("cuda", torch.cuda.current_device())
         if dist.get_backend(self.group) == "gloo":
             device = torch.device("cpu")
+        else:
+            device = torch.device("cuda", torch.cuda.current_device())
         local = torch.tensor(mine, dtype=torch.int32, device=device)
         gathered = [torch.empty_like(local) for _ in range(self.group_size)]
         dist.all_gather(gathered, local, self.group)

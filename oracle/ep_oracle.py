@@ -125,8 +125,8 @@ def fp8_dequant(q_u8: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """e4m3 bytes + per-128 scales -> bf16, the way the reference's test helper
     casts back (mooncake-wheel/tests/ep_test_utils.py:50-53)."""
     rows, H = q_u8.shape
-    f = q_u8.view(torch.float8_e4m3fn).to(torch.float32).view(rows, -1, 128)
-    return (f * scales.view(rows, -1, 1)).view(rows, H).to(torch.bfloat16)
+    f = q_u8.view(torch.float8_e4m3fn).to(torch.float32).view(rows, H // 128, 128)
+    return (f * scales.view(rows, H // 128, 1)).view(rows, H).to(torch.bfloat16)
 
 
 # --------------------------------------------------------------------------

@@ -1,0 +1,82 @@
+"""Host-side checks that need no GPU: the shared library loads, exports every
+entry point include/mcep.h declares, computes the buffer size hint like the
+reference, and fails loudly (no silent fallback) where a device is needed."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "mcep.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b(mcep_[a-z0-9_]+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    from mooncake_b200 import build
+    lib = ctypes.CDLL(build.build())
+    names = _declared_functions()
+    assert len(names) >= 25
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/mcep.h but not exported"
+
+
+def _reference_hint(M, H, R, E):
+    # mooncake-ep/include/mooncake_ep_buffer.h:42-61: two buffers, each with send and
+    # receive signals (E ints) and send and receive data (E*M*(2*16 + 2H) bytes)
+    sig = E * 4
+    data = E * M * (2 * 16 + H * 2)
+    return 4 * sig + 4 * data
+
+
+@pytest.mark.parametrize("M,H,R,E", [(128, 2048, 2, 16), (128, 7168, 8, 256), (4096, 7168, 8, 256),
+                                     (256, 4096, 8, 128), (4096, 4096, 8, 8), (1, 128, 1, 1)])
+def test_buffer_size_hint_matches_reference_formula(M, H, R, E):
+    from mooncake_b200 import Buffer, ep
+    assert ep.get_ep_buffer_size_hint(M, H, R, E) == _reference_hint(M, H, R, E)
+    assert Buffer.get_ep_buffer_size_hint(M, H, R, E) == _reference_hint(M, H, R, E)
+
+
+def test_survey_sizes():
+    from mooncake_b200 import ep
+    assert ep.get_ep_buffer_size_hint(128, 7168, 8, 256) == 1883246592       # config 2: 1.88 GB
+    assert round(ep.get_ep_buffer_size_hint(4096, 7168, 8, 256) / 1e9, 1) == 60.3  # config 3
+
+
+def test_module_surface_matches_reference_binding():
+    """Names the reference's pybind module and wrapper expose
+    (mooncake-ep/src/ep_py.cpp:14-46, mooncake_ep_buffer.py)."""
+    from mooncake_b200 import ep, mooncake_ep_buffer
+    assert ep.MAX_QP_COUNT == 256
+    for m in ("ibgda_disabled", "p2p_enabled", "use_fast_path", "update_local_qpns", "is_roce",
+              "sync_ibgda_peers", "get_mr_info", "get_gid", "get_local_qpns", "get_local_lids",
+              "get_ipc_handle", "sync_nvlink_ipc_handles", "dispatch", "combine"):
+        assert callable(getattr(ep.Buffer, m))
+    for m in ("current_stream_wait", "synchronize"):
+        assert callable(getattr(ep.EventHandle, m))
+    for m in ("connect", "update_ep_member", "get_ep_buffer_size_hint", "dispatch", "combine",
+              "get_next_combine_buffer"):
+        assert callable(getattr(mooncake_ep_buffer.Buffer, m))
+    assert callable(mooncake_ep_buffer.EventOverlap.current_stream_wait)
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-device behaviour")
+def test_no_device_is_a_loud_error_not_a_fallback():
+    from mooncake_b200 import ep
+    with pytest.raises(RuntimeError, match="CUDA error"):
+        ep.Buffer(0, 1, 1 << 20)
+
+
+def test_zero_copy_is_rejected_like_the_reference():
+    from mooncake_b200.mooncake_ep_buffer import Buffer
+    b = Buffer.__new__(Buffer)
+    with pytest.raises(NotImplementedError, match="zero-copy combine is not supported"):
+        b.get_next_combine_buffer(None)
+    with pytest.raises(NotImplementedError):
+        b.combine(None, None, None, None, 0, (), zero_copy=True)

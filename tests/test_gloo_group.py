@@ -1,0 +1,102 @@
+"""World-size-2 checks on CPU with the gloo backend: the handle exchange of
+`Buffer.connect()` (with the native runtime replaced by a recorder), and the
+oracle run rank by rank over a real process group against the golden vectors."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests.golden.make_golden import make_inputs, sha
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+class _RecorderRuntime:
+    """Stands in for mooncake_b200.ep.Buffer: records what the bootstrap hands it."""
+
+    def __init__(self, rank):
+        self.rank = rank
+        self.synced = None
+
+    def p2p_enabled(self):
+        return True
+
+    def get_ipc_handle(self):
+        return [self.rank * 100 + i for i in range(16)]
+
+    def sync_nvlink_ipc_handles(self, handles, mask):
+        self.synced = (handles, mask)
+
+    def use_fast_path(self):
+        return self.synced is not None
+
+
+def _connect_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import warnings
+    from mooncake_b200.mooncake_ep_buffer import Buffer
+    b = Buffer.__new__(Buffer)
+    b.rank, b.group_size, b.group, b.backend = rank, world, dist.group.WORLD, dist.group.WORLD
+    b.runtime = _RecorderRuntime(rank)
+    b._warned_active_ranks = False
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        b.connect()
+        b.update_ep_member()  # membership refresh re-runs the exchange
+    handles, mask = b.runtime.synced
+    ok = (handles == [[r * 100 + i for i in range(16)] for r in range(world)]
+          and mask == [1] * world
+          and sum("active_ranks is only available" in str(x.message) for x in w) == 1)
+    q.put((rank, ok))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_connect_exchanges_handles_in_rank_order():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_connect_worker, args=(r, 2, 29731, q)) for r in range(2)]
+    [p.start() for p in procs]
+    res = sorted(q.get(timeout=120) for _ in procs)
+    [p.join(60) for p in procs]
+    assert res == [(0, True), (1, True)]
+
+
+def _oracle_worker(rank, world, port, name, q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import ep_oracle as ora
+    g = torch.load(os.path.join(GOLDEN, f"{name}.pt"), weights_only=False)
+    cfg = g["ranks"][0]["cfg"]
+    x, idx, w = make_inputs(cfg, rank)
+    # every rank contributes its own tokens; the group gathers them (variable counts)
+    xs, idxs = [None] * world, [None] * world
+    dist.all_gather_object(xs, x)
+    dist.all_gather_object(idxs, idx)
+    mine = ora.dispatch(xs, idxs, cfg["M"], cfg["E"], cfg["fp8"], arith="fallback")[rank]
+    part = g["ranks"][rank]
+    L = cfg["E"] // world
+    ok = torch.equal(mine["recv_count"], part["recv_count"])
+    ok &= torch.equal(mine["layout_range"], part["layout_range"])
+    for le in range(L):
+        n = int(part["recv_count"][le])
+        ok &= torch.equal(mine["src_info"][le, :n], part["src_info"][le, :n])
+        ok &= sha(mine["recv_x"][le, :n]) == part["recv_x_sha"][le]
+    q.put((rank, bool(ok)))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name", ["c1_bf16", "small_fp8_uneven"])
+def test_oracle_over_a_real_group_matches_golden(name):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_oracle_worker, args=(r, 2, 29741 + len(name), name, q))
+             for r in range(2)]
+    [p.start() for p in procs]
+    res = sorted(q.get(timeout=180) for _ in procs)
+    [p.join(60) for p in procs]
+    assert res == [(0, True), (1, True)]
