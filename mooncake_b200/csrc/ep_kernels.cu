@@ -307,7 +307,9 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
     __shared__ int s_exp[kMaxTopk];
     __shared__ int s_slot[kMaxTopk];
     __shared__ int s_before[kMaxTopk];
+    __shared__ int s_raw[kMaxTopk];
     __shared__ int s_active[kMaxRanks];
+    __shared__ char* s_peer[kMaxRanks];
 
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
@@ -322,34 +324,54 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
 
     pdl_wait();
     pdl_launch_dependents();
+    // everything the block needs from memory is requested before the first
+    // barrier, so the routing work costs one memory round trip, not several
+    const int my_active = (!kDirect && tid < p.R) ? ld_volatile_s32(p.active_ranks + tid) : 1;
+    char* my_peer = (!kDirect && tid < p.R) ? reinterpret_cast<char*>(p.peer_base[tid]) : nullptr;
     if (kFused)
         for (int e = tid; e < p.E; e += nthr) hist[e] = 0;
     if (!kDirect) {
         for (int e = tid; e < p.E; e += nthr) cta_cnt[e] = 0;
-        if (tid < p.R) s_active[tid] = ld_volatile_s32(p.active_ranks + tid);
+        if (tid < p.R) s_active[tid] = my_active, s_peer[tid] = my_peer;
     }
-    __syncthreads();
 
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
         const char* xrow = xb + (size_t)t * p.H * 2;
-        // start the row load before the routing work
         V32 first = {};
         if (warp < ntiles && warp * 32 + lane < nchunks)
             first = ld32_readonly(xrow + (size_t)(warp * 32 + lane) * 32);
+        const bool scan_now = kFused && t == (int)blockIdx.x;
+        int ev[kMaxTopk];
+        if (scan_now && tid < p.T) {
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k)
+                ev[k] = k < p.K ? (int)__ldg(p.topk_idx + (size_t)tid * p.K + k) : -1;
+        }
+        int my_slot = -1;
         if (tid < kMaxTopk) {
-            s_exp[tid] = tid < p.K ? topk_entry(p.topk_idx, t, p.K, tid, p.E) : -1;
+            int e = tid < p.K ? (int)__ldg(p.topk_idx + (size_t)t * p.K + tid) : -1;
+            if (!kFused && tid < p.K) my_slot = __ldg(p.slot + (size_t)t * p.K + tid);
+            s_raw[tid] = (e >= 0 && e < p.E) ? e : -1;
             s_before[tid] = 0;
         }
         __syncthreads();
-        if (kFused && t == (int)blockIdx.x) {
+        if (tid < kMaxTopk) {
+            int e = s_raw[tid];
+            for (int kk = 0; kk < tid; ++kk)
+                if (s_raw[kk] == e) e = -1;  // a repeat of an earlier entry of this token
+            s_exp[tid] = e;
+        }
+        __syncthreads();
+        if (scan_now) {
             // one pass over the index matrix, one token per thread, entries in
             // registers: whole-batch histogram, and for this block's token the
             // number of earlier tokens per chosen expert
             for (int t2 = tid; t2 < p.T; t2 += nthr) {
-                int ev[kMaxTopk];
+                if (t2 != tid) {
 #pragma unroll
-                for (int k = 0; k < kMaxTopk; ++k)
-                    ev[k] = k < p.K ? (int)__ldg(p.topk_idx + (size_t)t2 * p.K + k) : -1;
+                    for (int k = 0; k < kMaxTopk; ++k)
+                        ev[k] = k < p.K ? (int)__ldg(p.topk_idx + (size_t)t2 * p.K + k) : -1;
+                }
 #pragma unroll
                 for (int k = 0; k < kMaxTopk; ++k) {
                     int e = ev[k];
@@ -371,7 +393,7 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
             int s = -1;
             const int e = s_exp[tid];
             if (e >= 0) {
-                s = kFused ? s_before[tid] : __ldg(p.slot + (size_t)t * p.K + tid);
+                s = kFused ? s_before[tid] : my_slot;
                 if (s >= p.M) {
                     atomicOr(p.status, kStatusSlotRange);
                 } else if (s >= 0) {
@@ -381,7 +403,7 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
                     } else {
                         const int dr = e / L;
                         if (s_active[dr])
-                            dst = reinterpret_cast<char*>(p.peer_base[dr]) + p.stage_off +
+                            dst = s_peer[dr] + p.stage_off +
                                   ((size_t)((e - dr * L) * p.R + p.rank) * p.M + s) * p.msg_stride;
                     }
                 }
@@ -459,8 +481,7 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
         } else if (c == 0) {
             const int dr = e / L;
             if (s_active[dr]) {
-                uint64_t* f = reinterpret_cast<uint64_t*>(
-                                  reinterpret_cast<char*>(p.peer_base[dr]) + p.flag_off) +
+                uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[dr] + p.flag_off) +
                               ((e - dr * L) * p.R + p.rank);
                 st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
             }
@@ -484,8 +505,7 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
                 p.done[e] = 0;
                 __threadfence();
                 const int dr = e / L;
-                uint64_t* f = reinterpret_cast<uint64_t*>(
-                                  reinterpret_cast<char*>(p.peer_base[dr]) + p.flag_off) +
+                uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[dr] + p.flag_off) +
                               ((e - dr * L) * p.R + p.rank);
                 st_relaxed_sys(f, ((uint64_t)p.seq << 32) | (uint32_t)(total + 1));
             }
@@ -544,7 +564,8 @@ __global__ void __launch_bounds__(1024) ep_dispatch_wait_kernel(DispatchWaitPara
 template <bool kFP8>
 __global__ void __launch_bounds__(512) ep_dispatch_pack_kernel(DispatchPackParams p) {
     extern __shared__ int smem_i32[];
-    int* pre = smem_i32;  // [L*R + 1]
+    int* pre = smem_i32;           // [L*R + 1] rows before each (expert, source)
+    int* beg = smem_i32 + p.L * p.R + 1;  // [L*R] first output row of each (expert, source)
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int n = p.L * p.R;
@@ -554,14 +575,17 @@ __global__ void __launch_bounds__(512) ep_dispatch_pack_kernel(DispatchPackParam
     const int S = p.H / 128;
     pdl_wait();
     pdl_launch_dependents();
-    for (int i = tid; i <= n; i += nthr) pre[i] = __ldcg(p.pack_prefix + i);
+    for (int i = tid; i <= n; i += nthr) {
+        pre[i] = __ldcg(p.pack_prefix + i);
+        if (i < n) beg[i] = (int)(__ldcg(p.layout_range + i) >> 32);
+    }
     __syncthreads();
     const int total = pre[n];
     for (int g = blockIdx.x; g < total; g += gridDim.x) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R;
         const int j = g - pre[i];
-        const int row = (int)(__ldcg(p.layout_range + i) >> 32) + j;
+        const int row = beg[i] + j;
         if (j >= p.M || row >= RM) {
             if (tid == 0) atomicOr(p.status, kStatusSlotRange);
             continue;
@@ -607,13 +631,17 @@ __global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams 
     const int nchunks = p.H / 16;
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
     __shared__ int s_active[kMaxRanks];
+    __shared__ char* s_peer[kMaxRanks];
     pdl_wait();
     pdl_launch_dependents();
     for (int i = tid; i < n; i += nthr) {
         pre[i] = (int)(__ldg(p.layout_range + i) & 0xffffffffll);
         cta_cnt[i] = 0;
     }
-    if (tid < p.R) s_active[tid] = ld_volatile_s32(p.active_ranks + tid);
+    if (tid < p.R) {
+        s_active[tid] = ld_volatile_s32(p.active_ranks + tid);
+        s_peer[tid] = reinterpret_cast<char*>(p.peer_base[tid]);
+    }
     __syncthreads();
     // empty segments: flag right away
     for (int i = blockIdx.x * nthr + tid; i < n; i += gridDim.x * nthr) {
@@ -621,7 +649,7 @@ __global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams 
             const int d = i % p.R, le = i / p.R;
             if (s_active[d]) {
                 uint64_t* f = reinterpret_cast<uint64_t*>(
-                                  reinterpret_cast<char*>(p.peer_base[d]) + p.flag_off) +
+                                  s_peer[d] + p.flag_off) +
                               (p.rank * p.L + le);
                 st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
             }
@@ -643,7 +671,7 @@ __global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams 
             if (tid == 0) atomicOr(p.status, kStatusBadSource);
         } else if (live) {
             const char* src = xb + ((size_t)le * RM + row) * p.H * 2;
-            char* dst = reinterpret_cast<char*>(p.peer_base[d]) + p.stage_off +
+            char* dst = s_peer[d] + p.stage_off +
                         ((size_t)(p.rank * p.L + le) * p.M + t) * p.H * 2;
             for (int tile = warp; tile < ntiles; tile += nwarps) {
                 const int c = tile * 32 + lane;
@@ -666,7 +694,7 @@ __global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams 
             if (s_active[d]) {
                 __threadfence();  // see the dispatch send kernel: one system fence per block
                 uint64_t* f = reinterpret_cast<uint64_t*>(
-                                  reinterpret_cast<char*>(p.peer_base[d]) + p.flag_off) +
+                                  s_peer[d] + p.flag_off) +
                               (p.rank * p.L + le);
                 st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
             }
@@ -730,17 +758,26 @@ __global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReducePar
     __shared__ int s_active[kMaxRanks];
     pdl_wait();
     pdl_launch_dependents();
-    if (tid < p.E / p.L) s_active[tid] = ld_volatile_s32(p.active_ranks + tid);
-    __syncthreads();
+    // the rank mask is requested together with the first token's routing entries
+    // (threads 32.. load it) so both arrive in one memory round trip
+    const int R = p.E / p.L;
+    if (tid >= 32 && tid < 32 + R) s_active[tid - 32] = ld_volatile_s32(p.active_ranks + tid - 32);
+    if (nthr < 32 + R) {  // tiny blocks (hidden <= 512): fall back to a separate pass
+        __syncthreads();
+        for (int r = tid; r < R; r += nthr) s_active[r] = ld_volatile_s32(p.active_ranks + r);
+    }
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+        int e = -1, r = 0;
+        float w = 0.f;
+        if (tid < p.K) {
+            e = (int)__ldg(p.topk_idx + (size_t)t * p.K + tid);
+            w = __ldg(p.topk_weights + (size_t)t * p.K + tid);
+            r = kDirect ? __ldcg(p.rowmap + (size_t)t * p.K + tid) : 0;
+        }
+        __syncthreads();  // s_active is in place (first pass), s_ptr is free (later passes)
         if (tid < kMaxTopk) {
             const char* ptr = nullptr;
-            float w = 0.f;
             if (tid < p.K) {
-                // independent loads first, so they overlap
-                const int e = (int)__ldg(p.topk_idx + (size_t)t * p.K + tid);
-                w = __ldg(p.topk_weights + (size_t)t * p.K + tid);
-                const int r = kDirect ? __ldcg(p.rowmap + (size_t)t * p.K + tid) : 0;
                 if (e >= 0 && e < p.E && s_active[e / p.L]) {
                     if (kDirect) {
                         if (r >= 0 && r < p.RM)
@@ -776,7 +813,6 @@ __global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReducePar
             st32(reinterpret_cast<char*>(p.combined_x) + ((size_t)t * p.H + (size_t)c * 16) * 2,
                  pack_bf16x16(acc));
         }
-        __syncthreads();
     }
 }
 
@@ -871,7 +907,7 @@ cudaError_t launch_dispatch_pack(const DispatchPackParams& p, const LaunchCtx& c
     // the row count is only known on the device: one wave of blocks that stride
     const int threads = block_threads(p.H);
     const int grid = persistent_grid((long long)p.L * p.R * p.M, threads, ctx);
-    const size_t smem = (size_t)(p.L * p.R + 1) * sizeof(int);
+    const size_t smem = (size_t)(2 * p.L * p.R + 1) * sizeof(int);
     auto k = p.use_fp8 ? ep_dispatch_pack_kernel<true> : ep_dispatch_pack_kernel<false>;
     return launch("ep_dispatch_pack", k, dim3(grid), dim3(threads), smem, ctx, p);
 }
