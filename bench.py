@@ -54,6 +54,8 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
     ap.add_argument("--e2e-steps", type=int, default=30)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-flush", action="store_true",
+                    help="diagnosis only: leave L2 warm between steps (numbers are not reportable)")
     ap.add_argument("--force-staged", action="store_true",
                     help="single rank: go through staging + flags like a multi-rank group")
     ap.add_argument("--inactive-rank", type=int, default=-1,
@@ -310,7 +312,8 @@ def run_ours(args):
     def step(ev=None):
         if i_am_out:
             return None
-        flush.zero_()
+        if not args.no_flush:
+            flush.zero_()
         align_ranks()
         if ev:
             ev[0].record()
@@ -318,7 +321,8 @@ def run_ours(args):
         if ev:
             ev[1].record()
         yy = expert(recv)
-        flush.zero_()
+        if not args.no_flush:
+            flush.zero_()
         align_ranks()
         if ev:
             ev[2].record()
@@ -491,7 +495,8 @@ def run_ours(args):
         "dtype": "fp8_e4m3+bf16" if w["fp8"] else "bf16", "data": "synthetic",
         "config": {"workload": f"{w['name']}: {w['desc']}", "tokens_per_rank": T, "hidden": H,
                    "experts": E, "experts_per_rank": L, "topk": K, "ranks": R,
-                   "l2": f"flushed before every dispatch and every combine ({L2_FLUSH_BYTES >> 20} MiB write)",
+                   "l2": ("NOT FLUSHED (diagnosis run)" if args.no_flush else
+                          f"flushed before every dispatch and every combine ({L2_FLUSH_BYTES >> 20} MiB write)"),
                    "timing": "CUDA events around dispatch and around combine, max over ranks per step, mean over steps",
                    "inactive_rank": inactive},
         "clocks": clocks, "gpu_launches": int(launches),

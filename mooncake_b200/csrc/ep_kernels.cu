@@ -72,7 +72,6 @@ std::string drain_kernel_times() {
 
 namespace kernels {
 
-constexpr int kWarpsPerBlock = 8;
 constexpr unsigned kFull = 0xffffffffu;
 
 template <typename... KArgs, typename... Args>
@@ -319,8 +318,9 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
     const int S = p.H / 128;
     const char* xb = reinterpret_cast<const char*>(p.x);
-    int* hist = smem_i32;                          // [E] whole-batch counts (fused)
-    int* cta_cnt = smem_i32 + (kFused ? p.E : 0);  // [E] sent by this block (staged)
+    int* hist = smem_i32;                              // [E] whole-batch counts (fused)
+    int* kmap = smem_i32 + p.E;                        // [E] expert -> k of this block's token (fused)
+    int* cta_cnt = smem_i32 + (kFused ? 2 * p.E : 0);  // [E] sent by this block (staged)
 
     pdl_wait();
     pdl_launch_dependents();
@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
     const int my_active = (!kDirect && tid < p.R) ? ld_volatile_s32(p.active_ranks + tid) : 1;
     char* my_peer = (!kDirect && tid < p.R) ? reinterpret_cast<char*>(p.peer_base[tid]) : nullptr;
     if (kFused)
-        for (int e = tid; e < p.E; e += nthr) hist[e] = 0;
+        for (int e = tid; e < p.E; e += nthr) hist[e] = 0, kmap[e] = -1;
     if (!kDirect) {
         for (int e = tid; e < p.E; e += nthr) cta_cnt[e] = 0;
         if (tid < p.R) s_active[tid] = my_active, s_peer[tid] = my_peer;
@@ -341,12 +341,13 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
         if (warp < ntiles && warp * 32 + lane < nchunks)
             first = ld32_readonly(xrow + (size_t)(warp * 32 + lane) * 32);
         const bool scan_now = kFused && t == (int)blockIdx.x;
-        int ev[kMaxTopk];
-        if (scan_now && tid < p.T) {
-#pragma unroll
-            for (int k = 0; k < kMaxTopk; ++k)
-                ev[k] = k < p.K ? (int)__ldg(p.topk_idx + (size_t)tid * p.K + k) : -1;
-        }
+        // the scan below lets a warp take whole tokens: lane -> (token, k)
+        const int tpw = 32 / p.K;            // tokens per warp pass (K <= 16)
+        const int sk = lane % p.K, st = lane / p.K;
+        const bool lane_used = st < tpw;
+        int e_first = -1;
+        if (scan_now && lane_used && warp * tpw + st < p.T)
+            e_first = (int)__ldg(p.topk_idx + (size_t)(warp * tpw + st) * p.K + sk);
         int my_slot = -1;
         if (tid < kMaxTopk) {
             int e = tid < p.K ? (int)__ldg(p.topk_idx + (size_t)t * p.K + tid) : -1;
@@ -360,30 +361,28 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
             for (int kk = 0; kk < tid; ++kk)
                 if (s_raw[kk] == e) e = -1;  // a repeat of an earlier entry of this token
             s_exp[tid] = e;
+            if (scan_now && e >= 0) kmap[e] = tid;
         }
         __syncthreads();
         if (scan_now) {
-            // one pass over the index matrix, one token per thread, entries in
-            // registers: whole-batch histogram, and for this block's token the
-            // number of earlier tokens per chosen expert
-            for (int t2 = tid; t2 < p.T; t2 += nthr) {
-                if (t2 != tid) {
-#pragma unroll
-                    for (int k = 0; k < kMaxTopk; ++k)
-                        ev[k] = k < p.K ? (int)__ldg(p.topk_idx + (size_t)t2 * p.K + k) : -1;
-                }
-#pragma unroll
-                for (int k = 0; k < kMaxTopk; ++k) {
-                    int e = ev[k];
-                    if (e >= p.E) e = -1;
-#pragma unroll
-                    for (int kk = 0; kk < k; ++kk)
-                        if (ev[kk] == e) e = -1;
-                    if (e < 0) continue;
+            // One pass over the index matrix with every warp: whole-batch
+            // histogram, and for this block's token the number of earlier tokens
+            // per chosen expert. A repeated expert inside a token is counted once
+            // (lanes holding the same (token, expert) elect the lowest lane).
+            for (int base = warp * tpw; base < p.T; base += nwarps * tpw) {
+                const int t2 = base + st;
+                const bool valid = lane_used && t2 < p.T;
+                int e = (base == warp * tpw) ? e_first
+                                             : (valid ? (int)__ldg(p.topk_idx + (size_t)t2 * p.K + sk) : -1);
+                if (!valid || e >= p.E) e = -1;
+                const unsigned key = e >= 0 ? (((unsigned)st << 16) | (unsigned)e) : (0x80000000u | lane);
+                const unsigned grp = __match_any_sync(kFull, key);
+                if (e >= 0 && (int)(__ffs(grp) - 1) == lane) {
                     atomicAdd(&hist[e], 1);
-                    if (t2 < t)
-                        for (int kk = 0; kk < p.K; ++kk)
-                            if (s_exp[kk] == e) atomicAdd(&s_before[kk], 1);
+                    if (t2 < t) {
+                        const int kk = kmap[e];
+                        if (kk >= 0) atomicAdd(&s_before[kk], 1);
+                    }
                 }
             }
             __syncthreads();
@@ -560,14 +559,18 @@ __global__ void __launch_bounds__(1024) ep_dispatch_wait_kernel(DispatchWaitPara
 // =============================================================================
 // dispatch: pack the staged messages into the caller's tensors
 // =============================================================================
-// One block per received row (blocks stride over the rows), one warp per tile.
+// One warp per received row (warps stride over the rows): the row's loads are
+// issued in batches before the stores, so a warp keeps several KB in flight and
+// the per-block prologue (row prefix of the segments) is paid once per SM.
+constexpr int kRowWarps = 8;
+
 template <bool kFP8>
-__global__ void __launch_bounds__(512) ep_dispatch_pack_kernel(DispatchPackParams p) {
+__global__ void __launch_bounds__(kRowWarps * 32) ep_dispatch_pack_kernel(DispatchPackParams p) {
     extern __shared__ int smem_i32[];
-    int* pre = smem_i32;           // [L*R + 1] rows before each (expert, source)
+    int* pre = smem_i32;                  // [L*R + 1] rows before each (expert, source)
     int* beg = smem_i32 + p.L * p.R + 1;  // [L*R] first output row of each (expert, source)
     const int tid = threadIdx.x, nthr = blockDim.x;
-    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+    const int lane = tid & 31, warp = tid >> 5;
     const int n = p.L * p.R;
     const int RM = p.R * p.M;
     const int nchunks = p.H / 16;
@@ -581,57 +584,89 @@ __global__ void __launch_bounds__(512) ep_dispatch_pack_kernel(DispatchPackParam
     }
     __syncthreads();
     const int total = pre[n];
-    for (int g = blockIdx.x; g < total; g += gridDim.x) {
+    for (int g = blockIdx.x * kRowWarps + warp; g < total; g += gridDim.x * kRowWarps) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R;
         const int j = g - pre[i];
         const int row = beg[i] + j;
         if (j >= p.M || row >= RM) {
-            if (tid == 0) atomicOr(p.status, kStatusSlotRange);
+            if (lane == 0) atomicOr(p.status, kStatusSlotRange);
             continue;
         }
         const char* msg = p.stage + ((size_t)i * p.M + j) * p.msg_stride;
         const size_t out_row = (size_t)le * RM + row;
-        for (int tile = warp; tile < ntiles; tile += nwarps) {
-            const int c = tile * 32 + lane;
-            if (c >= nchunks) continue;
-            if (kFP8)
-                st16(reinterpret_cast<char*>(p.recv_x) + out_row * p.H + (size_t)c * 16,
-                     ld16_coherent(msg + kHeaderBytes + (size_t)c * 16));
-            else
-                st32(reinterpret_cast<char*>(p.recv_x) + (out_row * p.H + (size_t)c * 16) * 2,
-                     ld32_coherent(msg + kHeaderBytes + (size_t)c * 32));
-        }
-        if (kFP8)
-            for (int gi = tid; gi < S; gi += nthr)
+        const int tok = lane == 0 ? ld_s32_coherent(msg) : 0;
+        if (kFP8) {
+            constexpr int kB = 16;  // tiles per batch: 16 x 16 B per lane in flight
+            char* out = reinterpret_cast<char*>(p.recv_x) + out_row * p.H;
+            float sc0 = 0.f, sc1 = 0.f;
+            if (lane < S) sc0 = ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)lane * 4);
+            if (lane + 32 < S) sc1 = ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)(lane + 32) * 4);
+            for (int t0 = 0; t0 < ntiles; t0 += kB) {
+                uint4 v[kB];
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks)
+                        v[b] = ld16_coherent(msg + kHeaderBytes + (size_t)c * 16);
+                }
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks) st16(out + (size_t)c * 16, v[b]);
+                }
+            }
+            if (lane < S) p.recv_scales[((size_t)le * S + lane) * RM + row] = sc0;
+            if (lane + 32 < S) p.recv_scales[((size_t)le * S + lane + 32) * RM + row] = sc1;
+            for (int gi = lane + 64; gi < S; gi += 32)  // hidden > 8192
                 p.recv_scales[((size_t)le * S + gi) * RM + row] =
                     ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)gi * 4);
-        if (tid == nthr - 1) p.recv_src_info[out_row] = ld_s32_coherent(msg);
+        } else {
+            constexpr int kB = 8;  // 8 x 32 B per lane in flight
+            char* out = reinterpret_cast<char*>(p.recv_x) + out_row * p.H * 2;
+            for (int t0 = 0; t0 < ntiles; t0 += kB) {
+                V32 v[kB];
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks)
+                        v[b] = ld32_coherent(msg + kHeaderBytes + (size_t)c * 32);
+                }
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks) st32(out + (size_t)c * 32, v[b]);
+                }
+            }
+        }
+        if (lane == 0) p.recv_src_info[out_row] = tok;
     }
 }
 
 // =============================================================================
 // combine: send expert outputs back to the token owners
 // =============================================================================
-// One block per packed row, one warp per tile. Row r of local expert le that
-// came from rank d's token t goes to d's combine staging slot [global expert][t]
-// (the slot rule of mooncake-ep/src/mooncake_ep_kernel.cu:633-637). Completion
-// is counted per (expert, destination) segment the same way dispatch counts per
-// expert: one system fence per block, then shared-memory counts are added to the
-// global ones and whoever completes a segment publishes that expert's flag at d.
-__global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams p) {
+// One warp per packed row (warps stride over the rows), loads batched ahead of
+// the stores. Row r of local expert le that came from rank d's token t goes to
+// d's combine staging slot [global expert][t] (the slot rule of
+// mooncake-ep/src/mooncake_ep_kernel.cu:633-637). Completion is counted per
+// (expert, destination) segment the same way dispatch counts per expert: one
+// system fence per block, then the block's shared-memory counts are added to
+// the global ones and whoever completes a segment publishes that expert's flag
+// at d.
+__global__ void __launch_bounds__(kRowWarps * 32) ep_combine_send_kernel(CombineSendParams p) {
     extern __shared__ int smem_i32[];
-    int* pre = smem_i32;                     // [L*R + 1]
+    int* pre = smem_i32;                      // [L*R + 1]
     int* cta_cnt = smem_i32 + p.L * p.R + 1;  // [L*R]
     __shared__ int s_wt[32];
+    __shared__ int s_active[kMaxRanks];
+    __shared__ char* s_peer[kMaxRanks];
     const int tid = threadIdx.x, nthr = blockDim.x;
-    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+    const int lane = tid & 31, warp = tid >> 5;
     const int n = p.L * p.R;
     const int RM = p.R * p.M;
     const int nchunks = p.H / 16;
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
-    __shared__ int s_active[kMaxRanks];
-    __shared__ char* s_peer[kMaxRanks];
     pdl_wait();
     pdl_launch_dependents();
     for (int i = tid; i < n; i += nthr) {
@@ -648,9 +683,7 @@ __global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams 
         if (pre[i] == 0) {
             const int d = i % p.R, le = i / p.R;
             if (s_active[d]) {
-                uint64_t* f = reinterpret_cast<uint64_t*>(
-                                  s_peer[d] + p.flag_off) +
-                              (p.rank * p.L + le);
+                uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[d] + p.flag_off) + (p.rank * p.L + le);
                 st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
             }
         }
@@ -659,26 +692,48 @@ __global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams 
     block_exclusive_scan(pre, n, s_wt);
     const int total = pre[n];
     const char* xb = reinterpret_cast<const char*>(p.x);
-    for (int g = blockIdx.x; g < total; g += gridDim.x) {
+    constexpr int kB = 8;  // 8 x 32 B per lane in flight: a 7168-wide row takes two round trips
+    for (int g = blockIdx.x * kRowWarps + warp; g < total; g += gridDim.x * kRowWarps) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R, d = i - le * p.R;
         const int j = g - pre[i];
         const int row = (int)(__ldg(p.layout_range + i) >> 32) + j;
         const bool live = s_active[d] != 0;
+        const bool row_ok = row < RM;
+        // the source row does not depend on the token index: request it together
+        // with the index so the two loads overlap
         int t = -1;
-        if (row < RM) t = __ldg(p.src_info + (size_t)le * RM + row);
+        if (row_ok) t = __ldg(p.src_info + (size_t)le * RM + row);
+        const char* src = xb + ((size_t)le * RM + (row_ok ? row : 0)) * p.H * 2;
+        V32 v[kB];
+#pragma unroll
+        for (int b = 0; b < kB; ++b) {
+            const int c = b * 32 + lane;
+            if (live && row_ok && b < ntiles && c < nchunks) v[b] = ld32_readonly(src + (size_t)c * 32);
+        }
         if (t < 0 || t >= p.M) {
-            if (tid == 0) atomicOr(p.status, kStatusBadSource);
+            if (lane == 0) atomicOr(p.status, kStatusBadSource);
         } else if (live) {
-            const char* src = xb + ((size_t)le * RM + row) * p.H * 2;
-            char* dst = s_peer[d] + p.stage_off +
-                        ((size_t)(p.rank * p.L + le) * p.M + t) * p.H * 2;
-            for (int tile = warp; tile < ntiles; tile += nwarps) {
-                const int c = tile * 32 + lane;
-                if (c < nchunks) st32(dst + (size_t)c * 32, ld32_readonly(src + (size_t)c * 32));
+            char* dst = s_peer[d] + p.stage_off + ((size_t)(p.rank * p.L + le) * p.M + t) * p.H * 2;
+#pragma unroll
+            for (int b = 0; b < kB; ++b) {
+                const int c = b * 32 + lane;
+                if (b < ntiles && c < nchunks) st32(dst + (size_t)c * 32, v[b]);
+            }
+            for (int t0 = kB; t0 < ntiles; t0 += kB) {
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks) v[b] = ld32_readonly(src + (size_t)c * 32);
+                }
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks) st32(dst + (size_t)c * 32, v[b]);
+                }
             }
         }
-        if (tid == 0) cta_cnt[i] += 1;
+        if (lane == 0) atomicAdd(&cta_cnt[i], 1);
     }
     __syncthreads();
     if (tid == 0) __threadfence_system();
@@ -693,9 +748,7 @@ __global__ void __launch_bounds__(512) ep_combine_send_kernel(CombineSendParams 
             const int d = i % p.R, le = i / p.R;
             if (s_active[d]) {
                 __threadfence();  // see the dispatch send kernel: one system fence per block
-                uint64_t* f = reinterpret_cast<uint64_t*>(
-                                  s_peer[d] + p.flag_off) +
-                              (p.rank * p.L + le);
+                uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[d] + p.flag_off) + (p.rank * p.L + le);
                 st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
             }
         }
@@ -878,7 +931,7 @@ bool dispatch_send_can_fuse_layout(int T, int K, int H, int num_sms) {
 cudaError_t launch_dispatch_send(const DispatchSendParams& p, const LaunchCtx& ctx) {
     const int threads = block_threads(p.H);
     int grid = p.fused ? (p.T > 0 ? p.T : 1) : persistent_grid(p.T, threads, ctx);
-    const size_t smem = (size_t)((p.fused ? p.E : 0) + (p.direct ? 0 : p.E)) * sizeof(int);
+    const size_t smem = (size_t)((p.fused ? 2 * p.E : 0) + (p.direct ? 0 : p.E)) * sizeof(int);
     void (*k)(DispatchSendParams) = nullptr;
     const int sel = (p.use_fp8 ? 4 : 0) | (p.direct ? 2 : 0) | (p.fused ? 1 : 0);
     switch (sel) {
@@ -905,16 +958,22 @@ cudaError_t launch_dispatch_wait(const DispatchWaitParams& p, const LaunchCtx& c
 
 cudaError_t launch_dispatch_pack(const DispatchPackParams& p, const LaunchCtx& ctx) {
     // the row count is only known on the device: one wave of blocks that stride
-    const int threads = block_threads(p.H);
-    const int grid = persistent_grid((long long)p.L * p.R * p.M, threads, ctx);
+    const int threads = kRowWarps * 32;
+    const long long rows = (long long)p.L * p.R * p.M;
+    const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, threads, ctx) > ctx.num_sms * 2
+                         ? ctx.num_sms * 2
+                         : persistent_grid((rows + kRowWarps - 1) / kRowWarps, threads, ctx);
     const size_t smem = (size_t)(2 * p.L * p.R + 1) * sizeof(int);
     auto k = p.use_fp8 ? ep_dispatch_pack_kernel<true> : ep_dispatch_pack_kernel<false>;
     return launch("ep_dispatch_pack", k, dim3(grid), dim3(threads), smem, ctx, p);
 }
 
 cudaError_t launch_combine_send(const CombineSendParams& p, const LaunchCtx& ctx) {
-    const int threads = block_threads(p.H);
-    const int grid = persistent_grid((long long)p.L * p.R * p.M, threads, ctx);
+    const int threads = kRowWarps * 32;
+    const long long rows = (long long)p.L * p.R * p.M;
+    const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, threads, ctx) > ctx.num_sms * 2
+                         ? ctx.num_sms * 2
+                         : persistent_grid((rows + kRowWarps - 1) / kRowWarps, threads, ctx);
     const size_t smem = (size_t)(2 * p.L * p.R + 1) * sizeof(int);
     return launch("ep_combine_send", ep_combine_send_kernel, dim3(grid), dim3(threads), smem, ctx, p);
 }
