@@ -219,6 +219,37 @@ int mcep_routing_layout(const int64_t* topk_idx, int num_tokens, int num_topk,
                         int32_t* rank_count, int32_t* expert_prefix,
                         int32_t* slot, void* scratch, uint64_t stream);
 
+/* ---- combine without any allocation -------------------------------------------
+ * No counterpart in the reference. For callers that are not allowed to allocate
+ * device memory (code that runs under a fixed device-memory budget, a serving
+ * loop that bans allocator calls once warm, a region owned by a memory pool):
+ * they cannot create an mcep_buffer, because creating one calls cudaMalloc.
+ * This is the single-rank combine (every expert local, num_ranks == 1) with
+ * its scratch - the (token, k) -> packed-row map - in a static device array
+ * that is part of the library image (about 256 KiB on every GPU that loads the
+ * library, held until the process exits). It calls no cudaMalloc, cudaFree or
+ * allocating library routine; the caller passes inputs and the output.
+ *   x            [E][M][H] bf16 expert outputs in the packed layout
+ *   src_info     [E][M], layout_range [E][1]: the handle of the dispatch
+ *   combined_x   [T][H] bf16
+ * Same result, bit for bit, as mcep_combine on a single-rank buffer.
+ * Limit: num_combined_tokens * num_topk <= MCEP_STATIC_MAX_ENTRIES, otherwise
+ * MCEP_ERR_INVALID with a message naming the limit.
+ * The first call on a device looks the array's device address up
+ * (cudaGetSymbolAddress) and writes two constants with cudaMemcpy; make that
+ * first call before any stream capture begins. All calls share the one array:
+ * two calls whose kernels overlap on the GPU (different streams, no ordering
+ * between them) race on it - order them. Errors of this entry point are read
+ * with mcep_static_last_error(). */
+#define MCEP_STATIC_MAX_ENTRIES 65536
+int mcep_combine_single_rank_static(const void* x, const int64_t* topk_idx,
+                                    const float* topk_weights, const int32_t* src_info,
+                                    const int64_t* layout_range, int num_experts,
+                                    int num_combined_tokens, int hidden, int num_topk,
+                                    int num_max_dispatch_tokens_per_rank,
+                                    void* combined_x, uint64_t stream);
+const char* mcep_static_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmcep.so")
-SOURCES = ["ep_kernels.cu", "ep_runtime.cu"]
+SOURCES = ["ep_kernels.cu", "ep_runtime.cu", "ep_noalloc.cu"]
 HEADERS = ["ep_kernels.cuh", "ep_device.cuh", os.path.join("..", "..", "include", "mcep.h")]
 
 

@@ -82,6 +82,9 @@ def _load() -> ctypes.CDLL:
         "mcep_hook_free": (i32, [vp]),
         "mcep_routing_layout_scratch_bytes": (_c.c_size_t, []),
         "mcep_routing_layout": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, u64]),
+        "mcep_combine_single_rank_static": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp,
+                                                  u64]),
+        "mcep_static_last_error": (_c.c_char_p, []),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -310,3 +313,24 @@ def routing_layout(topk_idx_ptr: int, num_tokens: int, num_topk: int, num_expert
 
 def routing_layout_scratch_bytes() -> int:
     return int(_lib.mcep_routing_layout_scratch_bytes())
+
+
+STATIC_MAX_ENTRIES = 65536  # MCEP_STATIC_MAX_ENTRIES
+
+
+def combine_single_rank_static(x_ptr: int, topk_idx_ptr: int, topk_weights_ptr: int,
+                               src_info_ptr: int, layout_range_ptr: int, num_experts: int,
+                               num_combined_tokens: int, hidden: int, num_topk: int,
+                               num_max_dispatch_tokens_per_rank: int, combined_x_ptr: int,
+                               stream_ptr: int = 0) -> None:
+    """Single-rank combine that allocates nothing (include/mcep.h:
+    mcep_combine_single_rank_static). For callers that may not call cudaMalloc and
+    therefore cannot construct a `Buffer`; the scratch is a static device array
+    shared by all calls, so calls that could overlap on the GPU must be ordered.
+    At most STATIC_MAX_ENTRIES (token, k) pairs."""
+    rc = _lib.mcep_combine_single_rank_static(x_ptr, topk_idx_ptr, topk_weights_ptr, src_info_ptr,
+                                              layout_range_ptr, num_experts, num_combined_tokens,
+                                              hidden, num_topk, num_max_dispatch_tokens_per_rank,
+                                              combined_x_ptr, stream_ptr)
+    if rc != 0:
+        raise RuntimeError(_lib.mcep_static_last_error().decode())
