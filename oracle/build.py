@@ -67,6 +67,7 @@ _MLX5_STUB = """\
 // Declaration-only stand-in for <infiniband/mlx5dv.h> (see verbs.h stub).
 #pragma once
 #include <stdint.h>
+#include <linux/types.h>
 #include <infiniband/verbs.h>
 struct mlx5_wqe_ctrl_seg { uint32_t opmod_idx_opcode; uint32_t qpn_ds;
                            uint8_t signature; uint8_t rsvd[2]; uint8_t fm_ce_se;
@@ -75,8 +76,8 @@ struct mlx5_wqe_raddr_seg { uint64_t raddr; uint32_t rkey; uint32_t reserved; };
 struct mlx5_wqe_data_seg { uint32_t byte_count; uint32_t lkey; uint64_t addr; };
 struct mlx5_wqe_atomic_seg { uint64_t swap_add; uint64_t compare; };
 struct mlx5_wqe_inl_data_seg { uint32_t byte_count; };
-struct mlx5_cqe64 { uint8_t rsvd0[60]; uint16_t wqe_counter; uint8_t signature;
-                    uint8_t op_own; };
+struct mlx5_cqe64 { uint8_t rsvd0[40]; uint64_t timestamp; uint8_t rsvd1[12];
+                    uint16_t wqe_counter; uint8_t signature; uint8_t op_own; };
 struct mlx5dv_devx_obj; struct mlx5dv_devx_umem; struct mlx5dv_devx_uar;
 enum { MLX5_WQE_CTRL_CQ_UPDATE = 2 << 2 };
 enum { MLX5_OPCODE_RDMA_WRITE = 0x08, MLX5_OPCODE_ATOMIC_FA = 0x12,
