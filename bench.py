@@ -104,7 +104,7 @@ def algorithmic_bytes(w, R, sel):
     b["ep_combine_reduce_direct"] = sel * 2 * H + T * 2 * H + 12 * T * K
     # staged (R > 1): every kernel reads its input once and writes its output once
     b["ep_dispatch_send"] = T * 2 * H + sel * msg
-    b["ep_dispatch_pack"] = 2 * sel * payload
+    b["ep_dispatch_recv"] = 2 * sel * payload
     b["ep_combine_send"] = 2 * sel * 2 * H
     b["ep_combine_reduce"] = sel * 2 * H + T * 2 * H
     return b

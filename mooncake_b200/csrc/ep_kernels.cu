@@ -21,6 +21,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <tuple>
 #include <vector>
 
 #include "ep_device.cuh"
@@ -158,28 +159,73 @@ __device__ __forceinline__ int find_segment(const int* pre, int n, int g) {
     return lo;
 }
 
-// Spin until the flag carries this call's sequence number. Leaves early when
-// the source is, or becomes, inactive: the rule of
-// mooncake-ep/src/mooncake_ep_kernel.cu:417-429 (timeout -> the waiter clears
-// active_ranks[src]; anyone who sees it cleared stops waiting). Returns the
-// flag's low word, or 0 when the wait was given up.
-__device__ __forceinline__ uint32_t wait_flag(const uint64_t* flag, uint32_t seq,
-                                              int32_t* active_ranks, int src,
-                                              int64_t timeout_ns, int64_t hard_ns,
-                                              int32_t* status) {
-    uint64_t v = ld_acquire_sys(flag);
-    if ((uint32_t)(v >> 32) == seq) return (uint32_t)v;
-    const uint64_t start = globaltimer_ns();
-    while (true) {
-        v = ld_acquire_sys(flag);
-        if ((uint32_t)(v >> 32) == seq) return (uint32_t)v;
-        const int64_t waited = (int64_t)(globaltimer_ns() - start);
-        if (timeout_ns >= 0 && waited > timeout_ns) st_volatile_s32(active_ranks + src, 0);
-        if (waited > hard_ns) {
-            st_volatile_s32(active_ranks + src, 0);
-            atomicOr(status, kStatusHardTimeout);
+// Decide one flag, once, for every block of the kernel.
+//
+// A flag is either seen to arrive (its word carries this call's sequence number)
+// or given up on (the rule of mooncake-ep/src/mooncake_ep_kernel.cu:417-429: after
+// `timeout` the waiter clears active_ranks[src]; whoever sees the entry cleared
+// stops waiting). Several blocks may need the same flag and they must agree, or
+// the receive layout would be torn; so the first block to reach a verdict
+// publishes it with a compare-and-swap into a local word, and every block -
+// including that one - takes the verdict from that word:
+//   resolved = seq << 32 | flag value     arrived
+//   resolved = seq << 32 | 0              given up
+// No block waits for another block: each keeps polling the peer's flag itself
+// until some verdict exists. Returns the flag's low word, or 0.
+__device__ __forceinline__ uint32_t resolve_flag(const WaitSpec& w, int i, int src,
+                                              bool primary = true) {
+    unsigned long long* res = reinterpret_cast<unsigned long long*>(w.resolved + i);
+    uint64_t start = 0;
+    if (!primary) {
+        // Many blocks want the same verdict. One of them (the "primary" for this
+        // flag) goes for the flag at once; the others look at the verdict word
+        // alone for a short while, which keeps hundreds of blocks from hammering
+        // one address with compare-and-swaps, and then fall back to doing the
+        // work themselves - they never depend on the primary making progress.
+        start = globaltimer_ns();
+        while (globaltimer_ns() - start < 4000) {
+            const uint64_t r = ld_acquire_gpu(w.resolved + i);
+            if ((uint32_t)(r >> 32) == w.seq) {
+                const uint32_t v = (uint32_t)r;
+                if (v) (void)ld_acquire_sys(w.flags + i);
+                return v;
+            }
         }
-        if (!ld_volatile_s32(active_ranks + src)) return 0;
+    }
+    while (true) {
+        // both words are requested together: one round trip in the common case
+        const uint64_t r = ld_acquire_gpu(w.resolved + i);
+        const uint64_t f = ld_acquire_sys(w.flags + i);
+        if ((uint32_t)(r >> 32) == w.seq) {
+            // decided already (possibly by another block). If it is an arrival,
+            // the flag load above was our own acquire of the sender's release -
+            // unless it raced ahead of the flag, then take it again.
+            const uint32_t v = (uint32_t)r;
+            if (v && (uint32_t)(f >> 32) != w.seq) (void)ld_acquire_sys(w.flags + i);
+            return v;
+        }
+        unsigned long long mine;
+        if ((uint32_t)(f >> 32) == w.seq) {
+            mine = (unsigned long long)f;  // arrived
+        } else {
+            const uint64_t now = globaltimer_ns();
+            if (start == 0) start = now;
+            const int64_t waited = (int64_t)(now - start);
+            if (w.timeout_ns >= 0 && waited > w.timeout_ns) st_volatile_s32(w.active_ranks + src, 0);
+            if (waited > w.hard_timeout_ns) {
+                st_volatile_s32(w.active_ranks + src, 0);
+                atomicOr(w.status, kStatusHardTimeout);
+            }
+            if (ld_volatile_s32(w.active_ranks + src)) continue;  // keep waiting
+            mine = (unsigned long long)w.seq << 32;               // given up
+        }
+        // first verdict wins; the value the swap returns is the winner's
+        const unsigned long long old = atomicCAS(res, (unsigned long long)r, mine);
+        const unsigned long long verdict = (old == (unsigned long long)r) ? mine : old;
+        if ((uint32_t)(verdict >> 32) != w.seq) continue;  // lost to a stale word: look again
+        const uint32_t v = (uint32_t)verdict;
+        if (v && (uint32_t)(f >> 32) != w.seq) (void)ld_acquire_sys(w.flags + i);
+        return v;
     }
 }
 
@@ -513,62 +559,22 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
 }
 
 // =============================================================================
-// dispatch: wait for the (source, expert) flags and fix the receive layout
+// dispatch: receive - wait for the (source, expert) flags, fix the layout, pack
 // =============================================================================
-// One block. Thread i waits for flag i = expert * R + source, then the block
-// turns the counts into `layout_range`, `recv_count` and the row prefix the
-// pack kernel partitions its work by.
-__global__ void __launch_bounds__(1024) ep_dispatch_wait_kernel(DispatchWaitParams p) {
-    extern __shared__ int smem_i32[];
-    int* cnt = smem_i32;              // [L*R]
-    int* tot = smem_i32 + p.L * p.R;  // [L + 1]
-    __shared__ int s_wt[32];
-    const int tid = threadIdx.x, nthr = blockDim.x;
-    const int n = p.L * p.R;
-    pdl_wait();
-    pdl_launch_dependents();
-    for (int i = tid; i < n; i += nthr) {
-        const int src = i % p.R;
-        const uint32_t v = wait_flag(p.flags + i, p.seq, p.active_ranks, src, p.timeout_ns,
-                                     p.hard_timeout_ns, p.status);
-        cnt[i] = v ? (int)v - 1 : 0;
-    }
-    __syncthreads();
-    for (int le = tid; le < p.L; le += nthr) {
-        int begin = 0;
-        for (int src = 0; src < p.R; ++src) {
-            const int c = cnt[le * p.R + src];
-            p.layout_range[le * p.R + src] = c ? (((int64_t)begin << 32) | (int64_t)c) : 0;
-            begin += c;
-        }
-        p.recv_count[le] = begin;
-        tot[le] = begin;
-    }
-    __syncthreads();
-    block_exclusive_scan(tot, p.L, s_wt);
-    for (int le = tid; le < p.L; le += nthr) {
-        int run = tot[le];
-        for (int src = 0; src < p.R; ++src) {
-            p.pack_prefix[le * p.R + src] = run;
-            run += cnt[le * p.R + src];
-        }
-    }
-    if (tid == 0) p.pack_prefix[n] = tot[p.L];
-}
-
-// =============================================================================
-// dispatch: pack the staged messages into the caller's tensors
-// =============================================================================
-// One warp per received row (warps stride over the rows): the row's loads are
-// issued in batches before the stores, so a warp keeps several KB in flight and
-// the per-block prologue (row prefix of the segments) is paid once per SM.
+// Every block first learns all L*R counts - one flag per thread, so the wait
+// costs one flag latency, and the verdict words make all blocks agree - and
+// turns them into the receive layout in shared memory: begin offsets per
+// (expert, source) and a global row prefix. Block 0 writes `layout_range` and
+// `recv_count`. Then rows are spread evenly over all warps of the grid (one
+// warp per row, loads batched ahead of stores), whatever the routing skew.
 constexpr int kRowWarps = 8;
 
 template <bool kFP8>
-__global__ void __launch_bounds__(kRowWarps * 32) ep_dispatch_pack_kernel(DispatchPackParams p) {
+__global__ void __launch_bounds__(kRowWarps * 32, 4) ep_dispatch_recv_kernel(DispatchRecvParams p) {
     extern __shared__ int smem_i32[];
     int* pre = smem_i32;                  // [L*R + 1] rows before each (expert, source)
     int* beg = smem_i32 + p.L * p.R + 1;  // [L*R] first output row of each (expert, source)
+    __shared__ int s_wt[32];
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int n = p.L * p.R;
@@ -578,11 +584,24 @@ __global__ void __launch_bounds__(kRowWarps * 32) ep_dispatch_pack_kernel(Dispat
     const int S = p.H / 128;
     pdl_wait();
     pdl_launch_dependents();
-    for (int i = tid; i <= n; i += nthr) {
-        pre[i] = __ldcg(p.pack_prefix + i);
-        if (i < n) beg[i] = (int)(__ldcg(p.layout_range + i) >> 32);
+    for (int i = tid; i < n; i += nthr) {
+        const uint32_t v = resolve_flag(p.w, i, i % p.R, (i % gridDim.x) == blockIdx.x);
+        pre[i] = v ? (int)v - 1 : 0;
     }
     __syncthreads();
+    for (int le = tid; le < p.L; le += nthr) {
+        int run = 0;
+        for (int src = 0; src < p.R; ++src) {
+            const int c = pre[le * p.R + src];
+            beg[le * p.R + src] = run;
+            if (blockIdx.x == 0)
+                p.layout_range[le * p.R + src] = c ? (((int64_t)run << 32) | (int64_t)c) : 0;
+            run += c;
+        }
+        if (blockIdx.x == 0) p.recv_count[le] = run;
+    }
+    __syncthreads();
+    block_exclusive_scan(pre, n, s_wt);
     const int total = pre[n];
     for (int g = blockIdx.x * kRowWarps + warp; g < total; g += gridDim.x * kRowWarps) {
         const int i = find_segment(pre, n, g);
@@ -590,14 +609,14 @@ __global__ void __launch_bounds__(kRowWarps * 32) ep_dispatch_pack_kernel(Dispat
         const int j = g - pre[i];
         const int row = beg[i] + j;
         if (j >= p.M || row >= RM) {
-            if (lane == 0) atomicOr(p.status, kStatusSlotRange);
+            if (lane == 0) atomicOr(p.w.status, kStatusSlotRange);
             continue;
         }
         const char* msg = p.stage + ((size_t)i * p.M + j) * p.msg_stride;
         const size_t out_row = (size_t)le * RM + row;
         const int tok = lane == 0 ? ld_s32_coherent(msg) : 0;
         if (kFP8) {
-            constexpr int kB = 16;  // tiles per batch: 16 x 16 B per lane in flight
+            constexpr int kB = 8;  // 8 x 16 B per lane in flight
             char* out = reinterpret_cast<char*>(p.recv_x) + out_row * p.H;
             float sc0 = 0.f, sc1 = 0.f;
             if (lane < S) sc0 = ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)lane * 4);
@@ -622,7 +641,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) ep_dispatch_pack_kernel(Dispat
                 p.recv_scales[((size_t)le * S + gi) * RM + row] =
                     ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)gi * 4);
         } else {
-            constexpr int kB = 8;  // 8 x 32 B per lane in flight
+            constexpr int kB = 4;  // 4 x 32 B per lane in flight
             char* out = reinterpret_cast<char*>(p.recv_x) + out_row * p.H * 2;
             for (int t0 = 0; t0 < ntiles; t0 += kB) {
                 V32 v[kB];
@@ -755,16 +774,6 @@ __global__ void __launch_bounds__(kRowWarps * 32) ep_combine_send_kernel(Combine
     }
 }
 
-// One block; thread e waits for expert e's flag
-// (mooncake-ep/src/mooncake_ep_kernel.cu:685-699).
-__global__ void __launch_bounds__(1024) ep_combine_wait_kernel(CombineWaitParams p) {
-    pdl_wait();
-    pdl_launch_dependents();
-    for (int e = threadIdx.x; e < p.E; e += blockDim.x)
-        (void)wait_flag(p.flags + e, p.seq, p.active_ranks, e / p.L, p.timeout_ns,
-                        p.hard_timeout_ns, p.status);
-}
-
 // Single rank: rowmap[t][k] = packed row of (token t, expert topk[t][k]) as the
 // handle records it.
 __global__ void __launch_bounds__(256) ep_combine_invert_kernel(CombineInvertParams p) {
@@ -808,17 +817,8 @@ __global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReducePar
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int nchunks = p.H / 16;
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
-    __shared__ int s_active[kMaxRanks];
     pdl_wait();
     pdl_launch_dependents();
-    // the rank mask is requested together with the first token's routing entries
-    // (threads 32.. load it) so both arrive in one memory round trip
-    const int R = p.E / p.L;
-    if (tid >= 32 && tid < 32 + R) s_active[tid - 32] = ld_volatile_s32(p.active_ranks + tid - 32);
-    if (nthr < 32 + R) {  // tiny blocks (hidden <= 512): fall back to a separate pass
-        __syncthreads();
-        for (int r = tid; r < R; r += nthr) s_active[r] = ld_volatile_s32(p.active_ranks + r);
-    }
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
         int e = -1, r = 0;
         float w = 0.f;
@@ -827,17 +827,20 @@ __global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReducePar
             w = __ldg(p.topk_weights + (size_t)t * p.K + tid);
             r = kDirect ? __ldcg(p.rowmap + (size_t)t * p.K + tid) : 0;
         }
-        __syncthreads();  // s_active is in place (first pass), s_ptr is free (later passes)
+        __syncthreads();  // the previous token's rows are done with s_ptr
         if (tid < kMaxTopk) {
             const char* ptr = nullptr;
-            if (tid < p.K) {
-                if (e >= 0 && e < p.E && s_active[e / p.L]) {
-                    if (kDirect) {
-                        if (r >= 0 && r < p.RM)
-                            ptr = reinterpret_cast<const char*>(p.x) + ((size_t)e * p.RM + r) * p.H * 2;
-                    } else {
+            if (tid < p.K && e >= 0 && e < p.E) {
+                const int owner = e / p.L;
+                if (kDirect) {
+                    if (ld_volatile_s32(p.active_ranks + owner) && r >= 0 && r < p.RM)
+                        ptr = reinterpret_cast<const char*>(p.x) + ((size_t)e * p.RM + r) * p.H * 2;
+                } else {
+                    // wait for this expert's rows (mooncake_ep_kernel.cu:685-699), then the
+                    // mask decides (an owner that timed out is skipped, :728-732)
+                    const uint32_t v = resolve_flag(p.w, e, owner);
+                    if (v && ld_volatile_s32(p.active_ranks + owner))
                         ptr = p.stage + ((size_t)e * p.M + t) * p.H * 2;
-                    }
                 }
             }
             s_ptr[tid] = ptr;
@@ -876,11 +879,31 @@ inline int block_threads(int H) {
     if (ntiles < 1) ntiles = 1;
     return ntiles * 32;
 }
-// a grid that fills the machine once (blocks stride over the work items)
-inline int persistent_grid(long long items, int threads, const LaunchCtx& ctx) {
-    int per_sm = 2048 / threads;
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 16) per_sm = 16;
+// a grid that fills the machine once (blocks stride over the work items):
+// as many blocks as are resident at a time for this kernel, block size and
+// shared memory
+template <typename K>
+inline int persistent_grid(long long items, K kernel, int threads, size_t smem, const LaunchCtx& ctx) {
+    // the occupancy query is not free: remember the answer per (kernel, block, smem)
+    static std::mutex mu;
+    static std::map<std::tuple<const void*, int, size_t>, int> cache;
+    int per_sm = 0;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        auto key = std::make_tuple(reinterpret_cast<const void*>(kernel), threads, smem);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            per_sm = it->second;
+        } else {
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) !=
+                    cudaSuccess ||
+                per_sm < 1) {
+                cudaGetLastError();
+                per_sm = 1;
+            }
+            cache[key] = per_sm;
+        }
+    }
     long long cap = (long long)ctx.num_sms * per_sm;
     long long g = items < cap ? items : cap;
     return (int)(g < 1 ? 1 : g);
@@ -922,15 +945,13 @@ cudaError_t launch_layout(const LayoutParams& p, const LaunchCtx& ctx) {
 bool dispatch_send_can_fuse_layout(int T, int K, int H, int num_sms) {
     // one block per token in a single wave, and an index matrix small enough to
     // be scanned by every block
-    const int threads = block_threads(H);
-    int per_sm = 2048 / threads;
-    if (per_sm > 16) per_sm = 16;
-    return (long long)T * K <= 4096 && T <= num_sms * per_sm;
+    (void)H;
+    // one block per token, all resident at once even at two blocks per SM
+    return (long long)T * K <= 4096 && T <= num_sms * 2;
 }
 
 cudaError_t launch_dispatch_send(const DispatchSendParams& p, const LaunchCtx& ctx) {
     const int threads = block_threads(p.H);
-    int grid = p.fused ? (p.T > 0 ? p.T : 1) : persistent_grid(p.T, threads, ctx);
     const size_t smem = (size_t)((p.fused ? 2 * p.E : 0) + (p.direct ? 0 : p.E)) * sizeof(int);
     void (*k)(DispatchSendParams) = nullptr;
     const int sel = (p.use_fp8 ? 4 : 0) | (p.direct ? 2 : 0) | (p.fused ? 1 : 0);
@@ -944,44 +965,33 @@ cudaError_t launch_dispatch_send(const DispatchSendParams& p, const LaunchCtx& c
         case 6: k = ep_dispatch_send_kernel<true, true, false>; break;
         default: k = ep_dispatch_send_kernel<true, true, true>; break;
     }
+    const int grid = p.fused ? (p.T > 0 ? p.T : 1) : persistent_grid(p.T, k, threads, smem, ctx);
     return launch(p.direct ? "ep_dispatch_send_direct" : "ep_dispatch_send", k, dim3(grid),
                   dim3(threads), smem, ctx, p);
 }
 
-cudaError_t launch_dispatch_wait(const DispatchWaitParams& p, const LaunchCtx& ctx) {
-    const int n = p.L * p.R;
-    int threads = 32;
-    while (threads < 1024 && threads < n) threads <<= 1;
-    const size_t smem = (size_t)(n + p.L + 1) * sizeof(int);
-    return launch("ep_dispatch_wait", ep_dispatch_wait_kernel, dim3(1), dim3(threads), smem, ctx, p);
-}
-
-cudaError_t launch_dispatch_pack(const DispatchPackParams& p, const LaunchCtx& ctx) {
-    // the row count is only known on the device: one wave of blocks that stride
+cudaError_t launch_dispatch_recv(const DispatchRecvParams& p, const LaunchCtx& ctx) {
     const int threads = kRowWarps * 32;
-    const long long rows = (long long)p.L * p.R * p.M;
-    const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, threads, ctx) > ctx.num_sms * 2
-                         ? ctx.num_sms * 2
-                         : persistent_grid((rows + kRowWarps - 1) / kRowWarps, threads, ctx);
     const size_t smem = (size_t)(2 * p.L * p.R + 1) * sizeof(int);
-    auto k = p.use_fp8 ? ep_dispatch_pack_kernel<true> : ep_dispatch_pack_kernel<false>;
-    return launch("ep_dispatch_pack", k, dim3(grid), dim3(threads), smem, ctx, p);
+    auto k = p.use_fp8 ? ep_dispatch_recv_kernel<true> : ep_dispatch_recv_kernel<false>;
+    // The row count is only known on the device. Under even routing a rank
+    // receives about what it sends (`expected_rows`); the grid is sized for
+    // twice that - blocks stride, so a skewed or larger load is still covered -
+    // and never beyond one resident wave.
+    long long rows = 2ll * p.expected_rows;
+    const long long worst = (long long)p.L * p.R * p.M;
+    if (rows > worst) rows = worst;
+    const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, k, threads, smem, ctx);
+    return launch("ep_dispatch_recv", k, dim3(grid), dim3(threads), smem, ctx, p);
 }
 
 cudaError_t launch_combine_send(const CombineSendParams& p, const LaunchCtx& ctx) {
     const int threads = kRowWarps * 32;
     const long long rows = (long long)p.L * p.R * p.M;
-    const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, threads, ctx) > ctx.num_sms * 2
-                         ? ctx.num_sms * 2
-                         : persistent_grid((rows + kRowWarps - 1) / kRowWarps, threads, ctx);
     const size_t smem = (size_t)(2 * p.L * p.R + 1) * sizeof(int);
+    const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, ep_combine_send_kernel,
+                                     threads, smem, ctx);
     return launch("ep_combine_send", ep_combine_send_kernel, dim3(grid), dim3(threads), smem, ctx, p);
-}
-
-cudaError_t launch_combine_wait(const CombineWaitParams& p, const LaunchCtx& ctx) {
-    int threads = 32;
-    while (threads < 1024 && threads < p.E) threads <<= 1;
-    return launch("ep_combine_wait", ep_combine_wait_kernel, dim3(1), dim3(threads), 0, ctx, p);
 }
 
 cudaError_t launch_combine_invert(const CombineInvertParams& p, const LaunchCtx& ctx) {
@@ -996,8 +1006,8 @@ cudaError_t launch_combine_invert(const CombineInvertParams& p, const LaunchCtx&
 
 cudaError_t launch_combine_reduce(const CombineReduceParams& p, const LaunchCtx& ctx) {
     const int threads = block_threads(p.H);
-    const int grid = persistent_grid(p.T, threads, ctx);
     auto k = p.direct ? ep_combine_reduce_kernel<true> : ep_combine_reduce_kernel<false>;
+    const int grid = persistent_grid(p.T, k, threads, 0, ctx);
     return launch(p.direct ? "ep_combine_reduce_direct" : "ep_combine_reduce", k, dim3(grid),
                   dim3(threads), 0, ctx, p);
 }

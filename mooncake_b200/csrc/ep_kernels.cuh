@@ -71,33 +71,31 @@ struct DispatchSendParams {
 bool dispatch_send_can_fuse_layout(int T, int K, int H, int num_sms);
 cudaError_t launch_dispatch_send(const DispatchSendParams& p, const LaunchCtx& ctx);
 
-struct DispatchWaitParams {
-    const uint64_t* flags;      // local dispatch flags of this parity, [L*R]
+// How a receive kernel waits for flags (see resolve_flag in ep_kernels.cu).
+struct WaitSpec {
+    const uint64_t* flags;      // local flags of this call's parity and direction
+    uint64_t* resolved;         // scratch, one word per flag: the verdict for this call
     int32_t* active_ranks;
-    int L, R;
     uint32_t seq;
     int64_t timeout_ns;         // < 0: only the hard bound applies
     int64_t hard_timeout_ns;
-    int32_t* recv_count;        // [L]
-    int64_t* layout_range;      // [L][R]
-    int32_t* pack_prefix;       // scratch [L*R + 1]: rows before each (expert, source)
     int32_t* status;
 };
-cudaError_t launch_dispatch_wait(const DispatchWaitParams& p, const LaunchCtx& ctx);
 
-struct DispatchPackParams {
+struct DispatchRecvParams {
+    WaitSpec w;                 // flags indexed expert * R + source
     const char* stage;          // local dispatch staging of this parity
-    const int32_t* pack_prefix; // [L*R + 1]
-    const int64_t* layout_range;
     int L, R, M, H;
     int use_fp8;
+    int expected_rows;          // host's estimate of the rows this rank receives (grid sizing)
     size_t msg_stride;
     void* recv_x;
     float* recv_scales;
     int32_t* recv_src_info;
-    int32_t* status;
+    int32_t* recv_count;        // [L]
+    int64_t* layout_range;      // [L][R]
 };
-cudaError_t launch_dispatch_pack(const DispatchPackParams& p, const LaunchCtx& ctx);
+cudaError_t launch_dispatch_recv(const DispatchRecvParams& p, const LaunchCtx& ctx);
 
 // ---- combine ----------------------------------------------------------------
 struct CombineSendParams {
@@ -115,16 +113,6 @@ struct CombineSendParams {
 };
 cudaError_t launch_combine_send(const CombineSendParams& p, const LaunchCtx& ctx);
 
-struct CombineWaitParams {
-    const uint64_t* flags;      // local combine flags of this parity, [E]
-    int32_t* active_ranks;
-    int E, L;
-    uint32_t seq;
-    int64_t timeout_ns, hard_timeout_ns;
-    int32_t* status;
-};
-cudaError_t launch_combine_wait(const CombineWaitParams& p, const LaunchCtx& ctx);
-
 // Single rank: (token, k) -> packed row, inverted from the handle.
 struct CombineInvertParams {
     const int32_t* src_info;    // [L][R*M]
@@ -141,7 +129,9 @@ struct CombineReduceParams {
     const float* topk_weights;  // [T][K]
     const int32_t* active_ranks;
     int T, K, E, L, M, H;
-    // staged: rows at stage + (expert * M + token) * 2H
+    // staged: waits for each needed expert's flag (w.flags indexed by global
+    // expert), then reads rows at stage + (expert * M + token) * 2H
+    WaitSpec w;
     const char* stage;
     // direct: rows at x + (expert * R*M + rowmap[t*K+k]) * 2H (single rank)
     int direct;

@@ -87,7 +87,8 @@ struct mcep_buffer {
 
     // workspace carve-up (per parity so two calls in flight do not share scratch)
     struct Scratch {
-        int32_t *slot, *count, *done, *pack_prefix, *cdone, *rowmap;
+        int32_t *slot, *count, *done, *cdone, *rowmap;
+        uint64_t *dres, *cres;  // verdict words of the receive kernels
         unsigned* ticket;
     } scratch[2];
     size_t scratch_entries = 0;  // capacity of slot/rowmap in int32
@@ -214,7 +215,7 @@ int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int
     b->status = reinterpret_cast<int32_t*>(b->workspace);
     const size_t small = (size_t)(MCEP_MAX_EXPERTS + 64) * sizeof(int32_t);
     const size_t half = (kWorkspaceBytes - 256) / 2;
-    const size_t big = (half - 4 * small - 256) / 2;  // bytes for each of slot / rowmap
+    const size_t big = (half - 7 * small - 256) / 2;  // bytes for each of slot / rowmap
     b->scratch_entries = big / sizeof(int32_t);
     for (int par = 0; par < 2; ++par) {
         char* w = b->workspace + 256 + par * half;
@@ -223,7 +224,8 @@ int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int
         w += 256;
         s.count = reinterpret_cast<int32_t*>(w), w += small;
         s.done = reinterpret_cast<int32_t*>(w), w += small;
-        s.pack_prefix = reinterpret_cast<int32_t*>(w), w += small;
+        s.dres = reinterpret_cast<uint64_t*>(w), w += 2 * small;
+        s.cres = reinterpret_cast<uint64_t*>(w), w += 2 * small;
         s.cdone = reinterpret_cast<int32_t*>(w), w += small;
         s.slot = reinterpret_cast<int32_t*>(w), w += big / 256 * 256;
         s.rowmap = reinterpret_cast<int32_t*>(w);
@@ -428,29 +430,24 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     MCEP_CUDA(mcep::launch_dispatch_send(sp, fused ? first : next));
 
     // receive phase, now or from the hook
-    mcep::DispatchWaitParams wp = {};
-    wp.flags = reinterpret_cast<const uint64_t*>(b->base + dflag_off);
-    wp.active_ranks = a->active_ranks, wp.L = g.L, wp.R = R, wp.seq = seq;
-    wp.timeout_ns = to_ns(a->timeout_us), wp.hard_timeout_ns = b->hard_timeout_ns;
-    wp.recv_count = a->packed_recv_count, wp.layout_range = a->packed_recv_layout_range;
-    wp.pack_prefix = sc.pack_prefix, wp.status = b->status;
-
-    mcep::DispatchPackParams pp = {};
-    pp.stage = b->base + data0, pp.pack_prefix = sc.pack_prefix;
-    pp.layout_range = a->packed_recv_layout_range;
+    mcep::DispatchRecvParams pp = {};
+    pp.w.flags = reinterpret_cast<const uint64_t*>(b->base + dflag_off);
+    pp.w.resolved = sc.dres, pp.w.active_ranks = a->active_ranks, pp.w.seq = seq;
+    pp.w.timeout_ns = to_ns(a->timeout_us), pp.w.hard_timeout_ns = b->hard_timeout_ns;
+    pp.w.status = b->status;
+    pp.stage = b->base + data0;
     pp.L = g.L, pp.R = R, pp.M = M, pp.H = H, pp.use_fp8 = fp8;
+    pp.expected_rows = T * K > 64 ? T * K : 64;
     pp.msg_stride = g.msg_stride, pp.recv_x = a->packed_recv_x;
     pp.recv_scales = a->packed_recv_x_scales, pp.recv_src_info = a->packed_recv_src_info;
-    pp.status = b->status;
+    pp.recv_count = a->packed_recv_count, pp.layout_range = a->packed_recv_layout_range;
 
     const bool pdl = b->pdl;
     const int num_sms = b->num_sms;
     auto recv = [=](cudaStream_t s, bool chained) -> int {
         if (direct) return MCEP_OK;
         mcep::LaunchCtx c0{s, num_sms, chained && pdl};
-        mcep::LaunchCtx c1{s, num_sms, pdl};
-        MCEP_CUDA(mcep::launch_dispatch_wait(wp, c0));
-        MCEP_CUDA(mcep::launch_dispatch_pack(pp, c1));
+        MCEP_CUDA(mcep::launch_dispatch_recv(pp, c0));
         return MCEP_OK;
     };
 
@@ -537,15 +534,13 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
         MCEP_CUDA(mcep::launch_combine_send(sp, first));
     }
 
-    mcep::CombineWaitParams wp = {};
-    wp.flags = reinterpret_cast<const uint64_t*>(b->base + cflag_off);
-    wp.active_ranks = a->active_ranks, wp.E = E, wp.L = g.L, wp.seq = seq;
-    wp.timeout_ns = to_ns(a->timeout_us), wp.hard_timeout_ns = b->hard_timeout_ns;
-    wp.status = b->status;
-
     mcep::CombineReduceParams rp = {};
     rp.topk_idx = a->topk_idx, rp.topk_weights = a->topk_weights, rp.active_ranks = a->active_ranks;
     rp.T = T, rp.K = K, rp.E = E, rp.L = g.L, rp.M = M, rp.H = H;
+    rp.w.flags = reinterpret_cast<const uint64_t*>(b->base + cflag_off);
+    rp.w.resolved = sc.cres, rp.w.active_ranks = a->active_ranks, rp.w.seq = seq;
+    rp.w.timeout_ns = to_ns(a->timeout_us), rp.w.hard_timeout_ns = b->hard_timeout_ns;
+    rp.w.status = b->status;
     rp.stage = b->base + cstage_off, rp.direct = direct, rp.x = a->x, rp.rowmap = sc.rowmap;
     rp.RM = g.RM, rp.combined_x = a->combined_x;
 
@@ -553,13 +548,7 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
     const int num_sms = b->num_sms;
     auto recv = [=](cudaStream_t s, bool chained) -> int {
         mcep::LaunchCtx c0{s, num_sms, chained && pdl};
-        mcep::LaunchCtx c1{s, num_sms, pdl};
-        if (!direct) {
-            MCEP_CUDA(mcep::launch_combine_wait(wp, c0));
-            MCEP_CUDA(mcep::launch_combine_reduce(rp, c1));
-        } else {
-            MCEP_CUDA(mcep::launch_combine_reduce(rp, c0));
-        }
+        MCEP_CUDA(mcep::launch_combine_reduce(rp, c0));
         return MCEP_OK;
     };
 
