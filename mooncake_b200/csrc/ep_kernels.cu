@@ -813,6 +813,7 @@ template <bool kDirect>
 __global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReduceParams p) {
     __shared__ const char* s_ptr[kMaxTopk];
     __shared__ float s_w[kMaxTopk];
+    __shared__ int s_row[kMaxTopk];
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int nchunks = p.H / 16;
@@ -825,11 +826,36 @@ __global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReducePar
         if (tid < p.K) {
             e = (int)__ldg(p.topk_idx + (size_t)t * p.K + tid);
             w = __ldg(p.topk_weights + (size_t)t * p.K + tid);
-            r = kDirect ? __ldcg(p.rowmap + (size_t)t * p.K + tid) : 0;
+            if (kDirect && !p.search) r = __ldcg(p.rowmap + (size_t)t * p.K + tid);
         }
-        __syncthreads();  // the previous token's rows are done with s_ptr
+        if (kDirect && p.search) {
+            // Small batches: no separate inversion pass. Warp k looks the token
+            // up in the handle itself - the segment of expert topk[t][k] that
+            // came from this (only) rank - 32 entries of src_info at a time.
+            for (int k = warp; k < p.K; k += nwarps) {
+                const int ek = (int)__ldg(p.topk_idx + (size_t)t * p.K + k);
+                int row = -1;
+                if (ek >= 0 && ek < p.E) {
+                    const long long lr = __ldg(p.layout_range + ek);
+                    const int cnt = (int)(lr & 0xffffffffll), begin = (int)(lr >> 32);
+                    for (int j0 = 0; j0 < cnt; j0 += 32) {
+                        const int j = begin + j0 + lane;
+                        const bool hit = j0 + lane < cnt && j < p.RM &&
+                                         __ldg(p.src_info + (size_t)ek * p.RM + j) == t;
+                        const unsigned m = __ballot_sync(kFull, hit);
+                        if (m) {
+                            row = begin + j0 + __ffs(m) - 1;
+                            break;
+                        }
+                    }
+                }
+                if (lane == 0) s_row[k] = row;
+            }
+        }
+        __syncthreads();  // s_row is in place; the previous token's rows are done with s_ptr
         if (tid < kMaxTopk) {
             const char* ptr = nullptr;
+            if (kDirect && p.search && tid < p.K) r = s_row[tid];
             if (tid < p.K && e >= 0 && e < p.E) {
                 const int owner = e / p.L;
                 if (kDirect) {

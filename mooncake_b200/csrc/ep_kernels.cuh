@@ -138,6 +138,10 @@ struct CombineReduceParams {
     const void* x;
     const int32_t* rowmap;
     int RM;
+    // direct + search: no rowmap; rows are looked up in the handle by the kernel
+    int search;
+    const int32_t* src_info;
+    const int64_t* layout_range;
     void* combined_x;           // [T][H] bf16
 };
 cudaError_t launch_combine_reduce(const CombineReduceParams& p, const LaunchCtx& ctx);

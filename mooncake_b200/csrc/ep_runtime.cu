@@ -519,13 +519,15 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
         if (int rc = order_after(stream, compute, b->ev_a)) return rc;
     mcep::LaunchCtx first{stream, b->num_sms, false};
 
-    if (direct) {
+    // small single-rank batches: the reduce kernel finds the rows in the handle itself
+    const bool search = direct && (long long)T * K <= 4096;
+    if (direct && !search) {
         mcep::CombineInvertParams ip = {};
         ip.src_info = a->src_info, ip.layout_range = a->layout_range, ip.topk_idx = a->topk_idx;
         ip.L = g.L, ip.R = R, ip.M = M, ip.T = T, ip.K = K, ip.rank = b->rank;
         ip.rowmap = sc.rowmap, ip.status = b->status;
         MCEP_CUDA(mcep::launch_combine_invert(ip, first));
-    } else {
+    } else if (!direct) {
         mcep::CombineSendParams sp = {};
         sp.x = a->x, sp.src_info = a->src_info, sp.layout_range = a->layout_range;
         sp.active_ranks = a->active_ranks, sp.peer_base = b->peer_dev, sp.done = sc.cdone;
@@ -543,11 +545,12 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
     rp.w.status = b->status;
     rp.stage = b->base + cstage_off, rp.direct = direct, rp.x = a->x, rp.rowmap = sc.rowmap;
     rp.RM = g.RM, rp.combined_x = a->combined_x;
+    rp.search = search, rp.src_info = a->src_info, rp.layout_range = a->layout_range;
 
     const bool pdl = b->pdl;
     const int num_sms = b->num_sms;
     auto recv = [=](cudaStream_t s, bool chained) -> int {
-        mcep::LaunchCtx c0{s, num_sms, chained && pdl};
+        mcep::LaunchCtx c0{s, num_sms, chained && pdl && !search};
         MCEP_CUDA(mcep::launch_combine_reduce(rp, c0));
         return MCEP_OK;
     };
