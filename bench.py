@@ -261,7 +261,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if R > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: a rendezvous mismatch must fail in a minute, not in ten
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
         group = dist.group.WORLD
     else:
         group = _Solo()
@@ -311,6 +313,10 @@ def run_ours(args):
 
     def step(ev=None):
         if i_am_out:
+            # inactive for the EP exchange only: it still takes part in the
+            # group's rendezvous collectives, or the others would wait for it
+            align_ranks()
+            align_ranks()
             return None
         if not args.no_flush:
             flush.zero_()
@@ -396,7 +402,9 @@ def run_ours(args):
     d2h = out_h.numel() * 2 + cnt_h.numel() * 4
     for i in range(args.e2e_steps + 3):
         if i_am_out:
-            break
+            align_ranks()
+            align_ranks()
+            continue
         align_ranks()
         torch.cuda.synchronize()
         t0 = time.perf_counter()

@@ -372,14 +372,18 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
     pdl_launch_dependents();
     // everything the block needs from memory is requested before the first
     // barrier, so the routing work costs one memory round trip, not several
-    const int my_active = (!kDirect && tid < p.R) ? ld_volatile_s32(p.active_ranks + tid) : 1;
-    char* my_peer = (!kDirect && tid < p.R) ? reinterpret_cast<char*>(p.peer_base[tid]) : nullptr;
     if (kFused)
         for (int e = tid; e < p.E; e += nthr) hist[e] = 0, kmap[e] = -1;
     if (!kDirect) {
         for (int e = tid; e < p.E; e += nthr) cta_cnt[e] = 0;
-        if (tid < p.R) s_active[tid] = my_active, s_peer[tid] = my_peer;
+        for (int r = tid; r < p.R; r += nthr) {  // a block may have as few as 32 threads
+            s_active[r] = ld_volatile_s32(p.active_ranks + r);
+            s_peer[r] = reinterpret_cast<char*>(p.peer_base[r]);
+        }
     }
+    // The tables above are read by other threads further down. The token loop
+    // has barriers of its own, but a block without tokens skips it.
+    __syncthreads();
 
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
         const char* xrow = xb + (size_t)t * p.H * 2;
@@ -692,9 +696,9 @@ __global__ void __launch_bounds__(kRowWarps * 32) ep_combine_send_kernel(Combine
         pre[i] = (int)(__ldg(p.layout_range + i) & 0xffffffffll);
         cta_cnt[i] = 0;
     }
-    if (tid < p.R) {
-        s_active[tid] = ld_volatile_s32(p.active_ranks + tid);
-        s_peer[tid] = reinterpret_cast<char*>(p.peer_base[tid]);
+    for (int r = tid; r < p.R; r += nthr) {
+        s_active[r] = ld_volatile_s32(p.active_ranks + r);
+        s_peer[r] = reinterpret_cast<char*>(p.peer_base[r]);
     }
     __syncthreads();
     // empty segments: flag right away

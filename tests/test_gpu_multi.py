@@ -42,5 +42,10 @@ def test_multi_gpu_parity(R):
            "--master-addr", "127.0.0.1", "--master-port", str(29620 + R),
            os.path.join(ROOT, "tests", "mp_worker.py")]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    tail = (p.stdout + p.stderr)[-4000:]
-    assert p.returncode == 0, tail
+    out = p.stdout + p.stderr
+    log_dir = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(log_dir):  # keep the whole log where a remote run brings it back
+        with open(os.path.join(log_dir, f"multi_gpu_parity_r{R}.log"), "w") as f:
+            f.write(out)
+    lines = [l for l in out.splitlines() if "FAILED" in l or "Error" in l or "assert" in l.lower()]
+    assert p.returncode == 0, "\n".join(lines[-30:]) + "\n" + out[-1500:]

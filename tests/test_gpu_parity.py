@@ -129,6 +129,12 @@ CASES = {
     "k1_l1": dict(R=4, T=32, M=32, H=256, E=4, K=1, fp8=True),
     # most choices a token may have
     "k16": dict(R=2, T=24, M=24, H=512, E=32, K=16, fp8=True, mask=20),
+    # the cases of the real 8-process run (tests/test_gpu_multi.py), as logical ranks
+    "r8_c1_bf16": dict(R=8, T=128, M=128, H=2048, E=16, K=4, fp8=False, routing="softmax"),
+    "r8_mixtral_t1": dict(R=8, T=1, M=4, H=4096, E=8, K=2, fp8=False),
+    "r8_mixtral_t1024": dict(R=8, T=1024, M=1024, H=4096, E=8, K=2, fp8=False),
+    "r8_ragged": dict(R=8, tokens=[(7 * r) % 50 for r in range(8)], M=64, H=640, E=64, K=3,
+                      fp8=True, mask=6),
 }
 
 
