@@ -253,11 +253,23 @@ __global__ void __launch_bounds__(1024)
     __syncthreads();
     pdl_wait();
     pdl_launch_dependents();
-    for (int i = tid; i < n; i += nthr) {
-        const int e = (int)__ldg(p.topk_idx + i);
-        if (e >= e0 && e < e1) {
-            const int t = i / p.K;
-            atomicOr(&mask[(e - e0) * words + (t >> 5)], 1u << (t & 31));
+    // Every block reads the whole index matrix; the loads are issued eight at a
+    // time so a pass costs a few memory round trips, not one per entry.
+    constexpr int kU = 8;
+    for (int i0 = tid; i0 < n; i0 += nthr * kU) {
+        int ev[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int i = i0 + u * nthr;
+            ev[u] = i < n ? (int)__ldg(p.topk_idx + i) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int e = ev[u];
+            if (e >= e0 && e < e1) {
+                const int t = (i0 + u * nthr) / p.K;
+                atomicOr(&mask[(e - e0) * words + (t >> 5)], 1u << (t & 31));
+            }
         }
     }
     __syncthreads();
@@ -279,16 +291,26 @@ __global__ void __launch_bounds__(1024)
         }
     }
     __syncthreads();
-    for (int i = tid; i < n; i += nthr) {
-        const int e = (int)__ldg(p.topk_idx + i);
-        if (e >= e0 && e < e1) {
-            const int t = i / p.K, k = i - t * p.K;
-            bool dup = false;
-            for (int kk = 0; kk < k; ++kk) dup |= ((int)__ldg(p.topk_idx + t * p.K + kk) == e);
-            const int o = (e - e0) * words + (t >> 5);
-            p.slot[i] = dup ? -1 : (int)(wpre[o] + __popc(mask[o] & ((1u << (t & 31)) - 1u)));
-        } else if (e < 0 && blockIdx.x == 0) {
-            p.slot[i] = -1;
+    for (int i0 = tid; i0 < n; i0 += nthr * kU) {
+        int ev[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int i = i0 + u * nthr;
+            ev[u] = i < n ? (int)__ldg(p.topk_idx + i) : -2;
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            const int i = i0 + u * nthr;
+            const int e = ev[u];
+            if (e >= e0 && e < e1) {
+                const int t = i / p.K, k = i - t * p.K;
+                bool dup = false;
+                for (int kk = 0; kk < k; ++kk) dup |= ((int)__ldg(p.topk_idx + t * p.K + kk) == e);
+                const int o = (e - e0) * words + (t >> 5);
+                p.slot[i] = dup ? -1 : (int)(wpre[o] + __popc(mask[o] & ((1u << (t & 31)) - 1u)));
+            } else if (e < 0 && i < n && blockIdx.x == 0) {
+                p.slot[i] = -1;
+            }
         }
     }
     if (p.rank_count == nullptr && p.expert_prefix == nullptr) return;
