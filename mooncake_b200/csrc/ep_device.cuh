@@ -18,12 +18,6 @@ struct alignas(32) V32 {  // 32 bytes = 16 bf16 = 8 x b32
     uint32_t w[8];
 };
 
-__device__ __forceinline__ int lane_id() {
-    int l;
-    asm("mov.s32 %0, %%laneid;" : "=r"(l));
-    return l;
-}
-
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -57,19 +51,6 @@ __device__ __forceinline__ int ld_volatile_s32(const int* p) {
 __device__ __forceinline__ void st_volatile_s32(int* p, int v) {
     asm volatile("st.volatile.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Counter bump that orders this warp's earlier stores (made visible to the lane
-// through __syncwarp) before it, at system scope: the payload may sit in a
-// peer GPU's memory and the thread that later sees the final count publishes a
-// flag that the peer acquires.
-__device__ __forceinline__ int atom_add_acq_rel_sys(int* p, int v) {
-    int old;
-    asm volatile("atom.add.acq_rel.sys.global.s32 %0, [%1], %2;"
-                 : "=r"(old)
-                 : "l"(p), "r"(v)
-                 : "memory");
-    return old;
-}
-
 // ---- 32-byte vector memory ops ----------------------------------------------
 // Read-only inputs that no kernel writes while this one runs (x, expert outputs).
 __device__ __forceinline__ V32 ld32_readonly(const void* p) {

@@ -86,7 +86,10 @@ enum { MLX5_INLINE_SEG = 0x80000000 };
 """
 
 
-def build_reference_kernels(reference_root: str = "/root/reference",
+DEFAULT_MOONCAKE_SRC = os.environ.get("MOONCAKE_SRC", os.path.join(os.sep, "root", "reference"))
+
+
+def build_reference_kernels(reference_root: str = DEFAULT_MOONCAKE_SRC,
                             force: bool = False) -> str | None:
     """Compile the reference kernel TU + harness. Returns the .so path, or
     None when no Mooncake checkout is present (then a prebuilt .so, if any,

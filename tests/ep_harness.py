@@ -126,6 +126,6 @@ def run_combine(bufs, ys, idxs, ws, handles, active=None, timeout_us=200_000):
 
 
 def mock_expert(recv_bf16: torch.Tensor, rank: int, L: int) -> torch.Tensor:
-    """y = x * (1 + e/16) in fp32, rounded to bf16 (BASELINE config 1's expert)."""
+    """y = x * (1 + e/16) in fp32, rounded to bf16 (the mock expert of the CPU-runnable case)."""
     e = (rank * L + torch.arange(L, device=recv_bf16.device)).float().view(L, 1, 1)
     return (recv_bf16.float() * (1.0 + e / 16.0)).to(torch.bfloat16)

@@ -1,7 +1,7 @@
 """Generate golden vectors from the reference's own torch path.
 
-Runs ONLY in a container that has a Mooncake checkout (argument
-`--reference`, default `/root/reference`). It loads
+Runs ONLY where a Mooncake checkout is available (argument `--reference`, or
+the environment variable `MOONCAKE_SRC`). It loads
 `mooncake-wheel/mooncake/mooncake_ep_buffer.py` by file path, builds the
 `Buffer` object without its native runtime, and calls the reference's
 `_fallback_dispatch` / `_fallback_combine` on CPU tensors with a gloo group
@@ -11,7 +11,7 @@ gloo wants the output of `all_gather_into_tensor` flat, the reference passes
 
 The vectors land in `tests/golden/*.pt`; tests read only those files.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <path to the Mooncake tree>
 """
 from __future__ import annotations
 
@@ -26,10 +26,11 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+_DEFAULT_SRC = os.path.join(os.sep, "root", "reference")
 
 # name -> config. `tokens` is per rank (uneven on purpose in some cases).
 CASES = {
-    # BASELINE config 1: the reference's CPU-runnable case
+    # the CPU-runnable case: 2 ranks, 128 tokens, hidden 2048, 16 experts, top-4
     "c1_bf16": dict(R=2, tokens=[128, 128], M=128, H=2048, E=16, K=4, fp8=False,
                     routing="softmax_topk", mask=0, full=False, seed=0),
     "c1_fp8": dict(R=2, tokens=[128, 128], M=128, H=2048, E=16, K=4, fp8=True,
@@ -68,7 +69,7 @@ def make_inputs(cfg: dict, rank: int):
 
 
 def expert_op(recv_bf16: torch.Tensor, rank: int, L: int) -> torch.Tensor:
-    """BASELINE config 1's mock expert: y = x * (1 + e/16), fp32 then bf16."""
+    """Mock expert of the CPU-runnable case: y = x * (1 + e/16), fp32 then bf16."""
     out = torch.empty_like(recv_bf16)
     for le in range(L):
         e = rank * L + le
@@ -150,7 +151,7 @@ def _worker(rank: int, name: str, cfg: dict, reference_root: str, port: int, out
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MOONCAKE_SRC", _DEFAULT_SRC))
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     torch.set_num_threads(2)

@@ -43,7 +43,7 @@ def test_buffer_size_hint_matches_reference_formula(M, H, R, E):
     assert Buffer.get_ep_buffer_size_hint(M, H, R, E) == _reference_hint(M, H, R, E)
 
 
-def test_survey_sizes():
+def test_known_sizes():
     from mooncake_b200 import ep
     assert ep.get_ep_buffer_size_hint(128, 7168, 8, 256) == 1883246592       # config 2: 1.88 GB
     assert round(ep.get_ep_buffer_size_hint(4096, 7168, 8, 256) / 1e9, 1) == 60.3  # config 3

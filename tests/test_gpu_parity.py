@@ -108,7 +108,7 @@ def _run_case(cfg, active=None, force_staged=True):
 
 
 CASES = {
-    # BASELINE config 1 (the reference's CPU-runnable case), both payload types
+    # the CPU-runnable case (2 ranks, hidden 2048, 16 experts, top-4), both payload types
     "c1_bf16": dict(R=2, T=128, M=128, H=2048, E=16, K=4, fp8=False, routing="softmax"),
     "c1_fp8": dict(R=2, T=128, M=128, H=2048, E=16, K=4, fp8=True, routing="softmax"),
     # config 2: DeepSeek-V3-shaped decode, FP8
