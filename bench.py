@@ -107,6 +107,9 @@ def algorithmic_bytes(w, R, sel):
     b["ep_dispatch_recv"] = 2 * sel * payload
     b["ep_combine_send"] = 2 * sel * 2 * H
     b["ep_combine_reduce"] = sel * 2 * H + T * 2 * H
+    # both phases of a call in one launch (small batches in a group)
+    b["ep_dispatch"] = b["ep_dispatch_send"] + b["ep_dispatch_recv"]
+    b["ep_combine"] = b["ep_combine_send"] + b["ep_combine_reduce"]
     return b
 
 

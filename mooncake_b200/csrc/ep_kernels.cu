@@ -368,8 +368,7 @@ __device__ __forceinline__ int topk_entry(const int64_t* topk_idx, int t, int K,
 }
 
 template <bool kFP8, bool kDirect, bool kFused>
-__global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParams p) {
-    extern __shared__ int smem_i32[];
+__device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, int* smem_i32) {
     __shared__ char* s_dst[kMaxTopk];
     __shared__ int s_exp[kMaxTopk];
     __shared__ int s_slot[kMaxTopk];
@@ -596,8 +595,7 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParam
 constexpr int kRowWarps = 8;
 
 template <bool kFP8>
-__global__ void __launch_bounds__(kRowWarps * 32, 4) ep_dispatch_recv_kernel(DispatchRecvParams p) {
-    extern __shared__ int smem_i32[];
+__device__ __forceinline__ void dispatch_recv_body(const DispatchRecvParams& p, int* smem_i32) {
     int* pre = smem_i32;                  // [L*R + 1] rows before each (expert, source)
     int* beg = smem_i32 + p.L * p.R + 1;  // [L*R] first output row of each (expert, source)
     __shared__ int s_wt[32];
@@ -629,7 +627,8 @@ __global__ void __launch_bounds__(kRowWarps * 32, 4) ep_dispatch_recv_kernel(Dis
     __syncthreads();
     block_exclusive_scan(pre, n, s_wt);
     const int total = pre[n];
-    for (int g = blockIdx.x * kRowWarps + warp; g < total; g += gridDim.x * kRowWarps) {
+    const int nwarps = nthr >> 5;
+    for (int g = blockIdx.x * nwarps + warp; g < total; g += gridDim.x * nwarps) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R;
         const int j = g - pre[i];
@@ -699,8 +698,7 @@ __global__ void __launch_bounds__(kRowWarps * 32, 4) ep_dispatch_recv_kernel(Dis
 // system fence per block, then the block's shared-memory counts are added to
 // the global ones and whoever completes a segment publishes that expert's flag
 // at d.
-__global__ void __launch_bounds__(kRowWarps * 32) ep_combine_send_kernel(CombineSendParams p) {
-    extern __shared__ int smem_i32[];
+__device__ __forceinline__ void combine_send_body(const CombineSendParams& p, int* smem_i32) {
     int* pre = smem_i32;                      // [L*R + 1]
     int* cta_cnt = smem_i32 + p.L * p.R + 1;  // [L*R]
     __shared__ int s_wt[32];
@@ -738,7 +736,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) ep_combine_send_kernel(Combine
     const int total = pre[n];
     const char* xb = reinterpret_cast<const char*>(p.x);
     constexpr int kB = 8;  // 8 x 32 B per lane in flight: a 7168-wide row takes two round trips
-    for (int g = blockIdx.x * kRowWarps + warp; g < total; g += gridDim.x * kRowWarps) {
+    const int nwarps = nthr >> 5;
+    for (int g = blockIdx.x * nwarps + warp; g < total; g += gridDim.x * nwarps) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R, d = i - le * p.R;
         const int j = g - pre[i];
@@ -836,7 +835,7 @@ __global__ void __launch_bounds__(256) ep_combine_invert_kernel(CombineInvertPar
 // channels: up to K 32-byte loads in flight, fp32 FMA accumulation in k order,
 // one bf16 rounding, one 32-byte store (mooncake_ep_kernel.cu:715-752).
 template <bool kDirect>
-__global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReduceParams p) {
+__device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p) {
     __shared__ const char* s_ptr[kMaxTopk];
     __shared__ float s_w[kMaxTopk];
     __shared__ int s_row[kMaxTopk];
@@ -922,6 +921,53 @@ __global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReducePar
                  pack_bf16x16(acc));
         }
     }
+}
+
+// =============================================================================
+// kernels
+// =============================================================================
+// The phases above as kernels of their own (hook mode, large batches), and the
+// two phases of a call as ONE kernel for small batches in a group: every block
+// first does its share of the send phase, then turns to the receive phase. The
+// receive phase waits for flags that this rank's own blocks publish at the end
+// of their send phase, so the grid is never larger than what is resident at
+// once (the launchers see to that); a block that has started never depends on a
+// block that has not.
+template <bool kFP8, bool kDirect, bool kFused>
+__global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParams p) {
+    extern __shared__ int smem_i32[];
+    dispatch_send_body<kFP8, kDirect, kFused>(p, smem_i32);
+}
+
+template <bool kFP8>
+__global__ void __launch_bounds__(kRowWarps * 32, 4) ep_dispatch_recv_kernel(DispatchRecvParams p) {
+    extern __shared__ int smem_i32[];
+    dispatch_recv_body<kFP8>(p, smem_i32);
+}
+
+template <bool kFP8>
+__global__ void __launch_bounds__(512) ep_dispatch_kernel(DispatchSendParams sp, DispatchRecvParams rp) {
+    extern __shared__ int smem_i32[];
+    dispatch_send_body<kFP8, false, true>(sp, smem_i32);
+    __syncthreads();
+    dispatch_recv_body<kFP8>(rp, smem_i32);
+}
+
+__global__ void __launch_bounds__(kRowWarps * 32) ep_combine_send_kernel(CombineSendParams p) {
+    extern __shared__ int smem_i32[];
+    combine_send_body(p, smem_i32);
+}
+
+template <bool kDirect>
+__global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReduceParams p) {
+    combine_reduce_body<kDirect>(p);
+}
+
+__global__ void __launch_bounds__(512) ep_combine_kernel(CombineSendParams sp, CombineReduceParams rp) {
+    extern __shared__ int smem_i32[];
+    combine_send_body(sp, smem_i32);
+    __syncthreads();
+    combine_reduce_body<false>(rp);
 }
 
 // threads per block: one warp per tile, at most 16 warps
@@ -1044,6 +1090,35 @@ cudaError_t launch_combine_send(const CombineSendParams& p, const LaunchCtx& ctx
     const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, ep_combine_send_kernel,
                                      threads, smem, ctx);
     return launch("ep_combine_send", ep_combine_send_kernel, dim3(grid), dim3(threads), smem, ctx, p);
+}
+
+bool call_can_be_one_kernel(int T, int K, int H, int num_sms) {
+    // small batch, one block per token resident at two blocks per SM (dispatch) and
+    // at one block per SM for the register-heavier combine
+    (void)H;
+    return (long long)T * K <= 4096 && T <= num_sms;
+}
+
+cudaError_t launch_dispatch_one_kernel(const DispatchSendParams& sp, const DispatchRecvParams& rp,
+                                       const LaunchCtx& ctx) {
+    const int threads = block_threads(sp.H);
+    size_t smem = (size_t)3 * sp.E * sizeof(int);
+    const size_t smem_recv = (size_t)(2 * rp.L * rp.R + 1) * sizeof(int);
+    if (smem_recv > smem) smem = smem_recv;
+    auto k = sp.use_fp8 ? ep_dispatch_kernel<true> : ep_dispatch_kernel<false>;
+    const int grid = sp.T > 0 ? sp.T : 1;
+    if (grid > persistent_grid(grid, k, threads, smem, ctx)) return cudaErrorInvalidConfiguration;
+    return launch("ep_dispatch", k, dim3(grid), dim3(threads), smem, ctx, sp, rp);
+}
+
+cudaError_t launch_combine_one_kernel(const CombineSendParams& sp, const CombineReduceParams& rp,
+                                      const LaunchCtx& ctx) {
+    const int threads = block_threads(sp.H);
+    const size_t smem = (size_t)(2 * sp.L * sp.R + 1) * sizeof(int);
+    // enough blocks for one token each in the reduce phase; the send phase strides
+    const int want = rp.T > 0 ? rp.T : 1;
+    const int grid = persistent_grid(want, ep_combine_kernel, threads, smem, ctx);
+    return launch("ep_combine", ep_combine_kernel, dim3(grid), dim3(threads), smem, ctx, sp, rp);
 }
 
 cudaError_t launch_combine_invert(const CombineInvertParams& p, const LaunchCtx& ctx) {

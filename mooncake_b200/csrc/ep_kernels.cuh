@@ -146,6 +146,13 @@ struct CombineReduceParams {
 };
 cudaError_t launch_combine_reduce(const CombineReduceParams& p, const LaunchCtx& ctx);
 
+// Both phases of a call in one launch (small batches in a group, no hook).
+bool call_can_be_one_kernel(int T, int K, int H, int num_sms);
+cudaError_t launch_dispatch_one_kernel(const DispatchSendParams& sp, const DispatchRecvParams& rp,
+                                       const LaunchCtx& ctx);
+cudaError_t launch_combine_one_kernel(const CombineSendParams& sp, const CombineReduceParams& rp,
+                                      const LaunchCtx& ctx);
+
 uint64_t kernel_launch_count();
 // Per-kernel device times: switch on, run, then drain "name launches total_ms" lines.
 void set_kernel_timing(bool on);

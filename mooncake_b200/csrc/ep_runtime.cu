@@ -73,6 +73,7 @@ struct mcep_buffer {
     bool force_staged = false;
     bool pdl = true;
     bool fuse_layout = true;
+    bool one_kernel = true;
     int64_t hard_timeout_ns = 10ll * 1000 * 1000 * 1000;
     char* base = nullptr;            // symmetric allocation: header region + data area
     char* workspace = nullptr;
@@ -338,6 +339,8 @@ int mcep_buffer_set_option(mcep_buffer* b, const char* name, int64_t value) {
         b->pdl = value != 0;
     } else if (!std::strcmp(name, "fuse_layout")) {
         b->fuse_layout = value != 0;
+    } else if (!std::strcmp(name, "one_kernel")) {
+        b->one_kernel = value != 0;
     } else {
         return fail(MCEP_ERR_INVALID, "Failed: unknown option '%s'", name);
     }
@@ -427,7 +430,6 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     sp.direct = direct, sp.recv_x = a->packed_recv_x, sp.recv_scales = a->packed_recv_x_scales;
     sp.recv_src_info = a->packed_recv_src_info;
     sp.recv_count = a->packed_recv_count, sp.layout_range = a->packed_recv_layout_range;
-    MCEP_CUDA(mcep::launch_dispatch_send(sp, fused ? first : next));
 
     // receive phase, now or from the hook
     mcep::DispatchRecvParams pp = {};
@@ -444,8 +446,23 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
 
     const bool pdl = b->pdl;
     const int num_sms = b->num_sms;
+    // Small batches in a group, no hook: both phases in one launch.
+    const bool one_kernel = fused && !direct && !a->return_recv_hook && b->one_kernel &&
+                            mcep::call_can_be_one_kernel(T, K, H, num_sms);
+    if (one_kernel) {
+        cudaError_t e1 = mcep::launch_dispatch_one_kernel(sp, pp, first);
+        if (e1 == cudaErrorInvalidConfiguration) {
+            cudaGetLastError();  // would not be resident at once on this device: two launches
+            MCEP_CUDA(mcep::launch_dispatch_send(sp, first));
+            MCEP_CUDA(mcep::launch_dispatch_recv(pp, next));
+        } else {
+            MCEP_CUDA(e1);
+        }
+    } else {
+        MCEP_CUDA(mcep::launch_dispatch_send(sp, fused ? first : next));
+    }
     auto recv = [=](cudaStream_t s, bool chained) -> int {
-        if (direct) return MCEP_OK;
+        if (direct || one_kernel) return MCEP_OK;
         mcep::LaunchCtx c0{s, num_sms, chained && pdl};
         MCEP_CUDA(mcep::launch_dispatch_recv(pp, c0));
         return MCEP_OK;
@@ -527,14 +544,15 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
         ip.L = g.L, ip.R = R, ip.M = M, ip.T = T, ip.K = K, ip.rank = b->rank;
         ip.rowmap = sc.rowmap, ip.status = b->status;
         MCEP_CUDA(mcep::launch_combine_invert(ip, first));
-    } else if (!direct) {
-        mcep::CombineSendParams sp = {};
-        sp.x = a->x, sp.src_info = a->src_info, sp.layout_range = a->layout_range;
-        sp.active_ranks = a->active_ranks, sp.peer_base = b->peer_dev, sp.done = sc.cdone;
-        sp.L = g.L, sp.R = R, sp.M = M, sp.H = H, sp.rank = b->rank;
-        sp.stage_off = cstage_off, sp.flag_off = cflag_off, sp.seq = seq, sp.status = b->status;
-        MCEP_CUDA(mcep::launch_combine_send(sp, first));
     }
+    mcep::CombineSendParams sp = {};
+    sp.x = a->x, sp.src_info = a->src_info, sp.layout_range = a->layout_range;
+    sp.active_ranks = a->active_ranks, sp.peer_base = b->peer_dev, sp.done = sc.cdone;
+    sp.L = g.L, sp.R = R, sp.M = M, sp.H = H, sp.rank = b->rank;
+    sp.stage_off = cstage_off, sp.flag_off = cflag_off, sp.seq = seq, sp.status = b->status;
+    const bool one_kernel = !direct && !a->return_recv_hook && b->one_kernel &&
+                            mcep::call_can_be_one_kernel(T, K, H, b->num_sms);
+    if (!direct && !one_kernel) MCEP_CUDA(mcep::launch_combine_send(sp, first));
 
     mcep::CombineReduceParams rp = {};
     rp.topk_idx = a->topk_idx, rp.topk_weights = a->topk_weights, rp.active_ranks = a->active_ranks;
@@ -549,7 +567,9 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
 
     const bool pdl = b->pdl;
     const int num_sms = b->num_sms;
+    if (one_kernel) MCEP_CUDA(mcep::launch_combine_one_kernel(sp, rp, first));
     auto recv = [=](cudaStream_t s, bool chained) -> int {
+        if (one_kernel) return MCEP_OK;
         mcep::LaunchCtx c0{s, num_sms, chained && pdl && !search};
         MCEP_CUDA(mcep::launch_combine_reduce(rp, c0));
         return MCEP_OK;
