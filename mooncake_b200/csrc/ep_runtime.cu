@@ -407,7 +407,9 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     mcep::LaunchCtx first{stream, b->num_sms, false};
     mcep::LaunchCtx next{stream, b->num_sms, b->pdl};
 
-    const bool fused = mcep::dispatch_send_can_fuse_layout(T, K, H, b->num_sms) && b->fuse_layout;
+    // (the in-kernel layout keeps three E-sized tables in shared memory)
+    const bool fused = mcep::dispatch_send_can_fuse_layout(T, K, H, b->num_sms) && b->fuse_layout &&
+                       E <= 2048;
     if (!fused) {
         mcep::LayoutParams lp = {};
         lp.topk_idx = a->topk_idx;
