@@ -33,6 +33,13 @@ def run_case(cfg, group, rank, R, buf_cache):
         buf_cache.clear()
         buf_cache[key] = Buffer(group, nbytes)
     buf = buf_cache[key]
+    if cfg.get("refresh_members"):
+        # membership refresh (Buffer.update_ep_member): every rank re-exports and
+        # re-imports the handles together, with nothing in flight
+        torch.cuda.synchronize()
+        dist.barrier()
+        buf.update_ep_member()
+        dist.barrier()
     if not active[rank]:
         return  # an inactive rank makes no call
     x, idx, w = xs[rank].cuda(), idxs[rank].cuda(), ws[rank].cuda()

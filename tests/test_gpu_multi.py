@@ -19,6 +19,9 @@ def _cases(R):
         "decode_fp8_async": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, mode="async", seed=2),
         "decode_fp8_hook": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, mode="hook", seed=3),
         "zipf_fp8": dict(T=256, M=256, H=4096, E=128, K=8, fp8=True, routing="zipf1.2"),
+        # same buffer as the case before, after a membership refresh
+        "zipf_fp8_after_refresh": dict(T=256, M=256, H=4096, E=128, K=8, fp8=True,
+                                       routing="zipf1.2", seed=4, refresh_members=True),
         "mixtral_t1": dict(T=1, M=4, H=4096, E=8, K=2, fp8=False),
         "mixtral_t1024": dict(T=1024, M=1024, H=4096, E=8, K=2, fp8=False),
         "ragged": dict(tokens=[(7 * r) % 50 for r in range(R)], M=64, H=640, E=8 * R, K=3,
