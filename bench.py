@@ -375,7 +375,6 @@ def run_ours(args):
         step(evs[i])
     barrier()
     t_wall = time.perf_counter() - t_wall0
-    clocks = sampler.stop() if sampler else None
     launches = ep.kernel_launch_count() - launches0
     if i_am_out:
         td = torch.zeros(K_steps, device=dev)
@@ -398,6 +397,10 @@ def run_ours(args):
     barrier()
     ktimes = ep.drain_kernel_times()
     ep.set_kernel_timing(False)
+    # the sampler covers the timed region and the per-kernel pass that follows it
+    # (same steps, same load); the timed region alone is too short for more than a
+    # couple of nvidia-smi samples
+    clocks = sampler.stop() if sampler else None
 
     # ---- end to end: host buffers in, host buffers out ------------------------------------
     e2e_times = []
