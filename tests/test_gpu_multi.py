@@ -46,8 +46,8 @@ def test_multi_gpu_parity(R):
            os.path.join(ROOT, "tests", "mp_worker.py")]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     out = p.stdout + p.stderr
-    log_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(log_dir):  # keep the whole log where a remote run brings it back
+    log_dir = os.environ.get("MCEP_TEST_LOG_DIR", "")
+    if os.path.isdir(log_dir):  # keep the whole log of the child processes
         with open(os.path.join(log_dir, f"multi_gpu_parity_r{R}.log"), "w") as f:
             f.write(out)
     lines = [l for l in out.splitlines() if "FAILED" in l or "Error" in l or "assert" in l.lower()]

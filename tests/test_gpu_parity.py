@@ -26,6 +26,8 @@ def _inputs(cfg):
     for r in range(R):
         x, idx, w = make_rank_inputs(cfg.get("seed", 1), r, tokens[r], cfg["H"], cfg["E"],
                                      cfg["K"], cfg.get("routing", "uniform"), cfg.get("mask", 0))
+        if cfg.get("mask_all"):
+            idx.fill_(-1)
         xs.append(x), idxs.append(idx), ws.append(w)
     return xs, idxs, ws
 
@@ -129,6 +131,13 @@ CASES = {
     "k1_l1": dict(R=4, T=32, M=32, H=256, E=4, K=1, fp8=True),
     # most choices a token may have
     "k16": dict(R=2, T=24, M=24, H=512, E=32, K=16, fp8=True, mask=20),
+    # nothing to send at all: no tokens anywhere, and tokens whose every choice is masked
+    "all_empty": dict(R=2, tokens=[0, 0], M=8, H=128, E=4, K=2, fp8=True),
+    "all_masked": dict(R=2, T=8, M=8, H=128, E=4, K=2, fp8=False, mask_all=True),
+    # fewer tokens than the per-rank maximum the buffers are laid out for
+    "m_above_t": dict(R=2, T=5, M=32, H=256, E=8, K=2, fp8=True),
+    # the largest expert count the library takes (routing layout in its own kernel)
+    "experts_4096": dict(R=2, T=64, M=64, H=128, E=4096, K=8, fp8=True),
     # the cases of the real 8-process run (tests/test_gpu_multi.py), as logical ranks
     "r8_c1_bf16": dict(R=8, T=128, M=128, H=2048, E=16, K=4, fp8=False, routing="softmax"),
     "r8_mixtral_t1": dict(R=8, T=1, M=4, H=4096, E=8, K=2, fp8=False),

@@ -238,7 +238,7 @@ def test_time_reference_kernels_beside_ours_single_gpu():
                     "reference side = its two launchers with preallocated outputs, "
                     "our side = the full Buffer.dispatch/combine call")
     print("REFERENCE_KERNEL_TIMING " + json.dumps(out))
-    d = os.path.join(ROOT, "gpurun_out")
+    d = os.environ.get("MCEP_TEST_LOG_DIR", "")
     if os.path.isdir(d):
         with open(os.path.join(d, "ref_kernel_timing.json"), "w") as f:
             json.dump(out, f, indent=1)

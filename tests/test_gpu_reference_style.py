@@ -1,0 +1,146 @@
+"""The checks of the reference's own EP test, re-expressed for this library.
+
+The reference test (mooncake-wheel/tests/test_mooncake_ep.py:27-99) feeds
+self-describing payloads - every channel but the last 128 carries a code of the
+source rank, the last 128 carry the token index - and then checks, per local
+expert: the received count against the gathered routing (:63-64), every row
+against its `src_info` and the `layout_range` segment of its source rank
+(:66-75), the combine result against the closed form `x * sum(valid weights)`
+(:92-94, difference below 1e-5), and that repeating a call gives the same
+bytes (:77-80). Here the ranks of a group run one after the other on one GPU
+(all sends first, then all receives).
+"""
+from __future__ import annotations
+
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from ep_harness import FakeGroup, local_group  # noqa: E402
+from mooncake_b200 import Buffer  # noqa: E402
+
+RANK_OFFSET = 128  # codes rank - 128 .. stay exact in bf16 and in e4m3 * scale
+
+
+def _inputs(rank: int, T: int, H: int, E: int, K: int, seed: int):
+    g = torch.Generator().manual_seed(seed + rank)
+    x = torch.ones((T, H), dtype=torch.bfloat16) * (rank - RANK_OFFSET)
+    x[:, -128:] = torch.arange(T).to(torch.bfloat16).view(-1, 1)
+    scores = torch.randn((T, E), generator=g).abs() + 1
+    idx = torch.topk(scores, K, dim=-1, largest=True, sorted=True)[1].contiguous()
+    w = torch.randn((T, K), generator=g).abs().contiguous()
+    rnd = random.Random(seed * 131 + rank)
+    for _ in range(10):
+        idx[rnd.randint(0, T - 1), rnd.randint(0, K - 1)] = -1
+    return x.cuda(), idx.cuda(), w.cuda()
+
+
+def _cast_back(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    n, h = q.shape
+    return (q.float().view(n, -1, 128) * scales.reshape(n, -1, 1)).view(n, h).to(torch.bfloat16)
+
+
+def _similarity_gap(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.double() + 1, b.double() + 1
+    return float(1 - 2 * (a * b).sum() / (a * a + b * b).sum())
+
+
+def _digest(t: torch.Tensor) -> int:
+    """Position-weighted sum of the tensor's bytes."""
+    if t.numel() == 0:
+        return 0
+    b = t.reshape(-1).contiguous().view(torch.uint8).to(torch.int64)
+    return int((b * (torch.arange(b.numel(), device=b.device) % 8191 + 1)).sum())
+
+
+def _layer(bufs, xs, idxs, ws, T, E, use_fp8):
+    """One dispatch + combine over the whole group; returns per-rank results."""
+    R = len(bufs)
+    H = xs[0].size(1)
+    # the reference test passes a mask of the wrong length (one entry per token);
+    # the wrapper then treats every rank as active
+    active = torch.ones((T,), dtype=torch.int32, device="cuda")
+    pend = []
+    for r in range(R):
+        pend.append(bufs[r].dispatch(xs[r], idxs[r], active, T, E, -1, use_fp8=use_fp8,
+                                     return_recv_hook=True))
+    for p in pend:
+        p[4]()
+    torch.cuda.synchronize()
+    sims = []
+    for r in range(R):
+        rx = pend[r][0]
+        if use_fp8:
+            q, s = rx[0], rx[1].contiguous()
+            sims.append(_cast_back(q.view(-1, H), s.view(-1, H // 128)).view(q.shape))
+        else:
+            sims.append(rx.clone())
+    cpend = []
+    for r in range(R):
+        out = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+        cpend.append(bufs[r].combine(sims[r], idxs[r], ws[r], active, -1, pend[r][2],
+                                     return_recv_hook=True, out=out))
+    for c in cpend:
+        c[2]()
+    torch.cuda.synchronize()
+    return pend, sims, [c[0] for c in cpend]
+
+
+def _check_layer(R, T, H, E, K, use_fp8, bufs, seed):
+    L = E // R
+    ins = [_inputs(r, T, H, E, K, seed) for r in range(R)]
+    xs, idxs, ws = [i[0] for i in ins], [i[1] for i in ins], [i[2] for i in ins]
+    all_idx = torch.stack(idxs)  # what the reference test all-gathers
+    digests = []
+    for _ in range(2):  # twice: the second pass must reproduce the first, byte for byte
+        pend, sims, combined = _layer(bufs, xs, idxs, ws, T, E, use_fp8)
+        dig = 0
+        for r in range(R):
+            rx, cnt, handle = pend[r][0], pend[r][1], pend[r][2]
+            for i in range(L):
+                e = r * L + i
+                n = int(cnt[i])
+                lr = handle[1][i]
+                assert n == int((lr & 0xFFFFFFFF).sum())
+                assert n == int((all_idx == e).sum())
+                rows = sims[r][i, :n].float()
+                src = handle[0][i, :n]
+                lo, hi = rows[:, :-128].amin(dim=-1), rows[:, :-128].amax(dim=-1)
+                assert torch.equal(lo, hi)
+                assert float((rows[:, -128:] - (src.view(-1, 1) % T).float()).abs().sum()) == 0
+                for j in range(R):
+                    begin, count = int(lr[j] >> 32), int(lr[j] & 0xFFFFFFFF)
+                    assert int((lo == j - RANK_OFFSET).sum()) == int((all_idx[j] == e).sum())
+                    assert count == int((all_idx[j] == e).sum())
+                    seg = rows[begin:begin + count, :-128]
+                    assert float((seg - (j - RANK_OFFSET)).abs().sum()) == 0
+                if use_fp8:
+                    dig ^= _digest(rx[0][i, :n]) ^ _digest(rx[1][i, :n].contiguous())
+                else:
+                    dig ^= _digest(rx[i, :n])
+            want = xs[r].float() * ws[r].masked_fill(idxs[r] == -1, 0).sum(dim=1).view(-1, 1)
+            assert int(torch.isnan(combined[r]).sum()) == 0
+            gap = _similarity_gap(want, combined[r].float())
+            assert gap < 1e-5, f"rank {r}: {gap=}"
+            dig ^= _digest(combined[r])
+        digests.append(dig)
+    assert digests[0] == digests[1]
+
+
+@pytest.mark.parametrize("use_fp8", [False, True])
+@pytest.mark.parametrize("R,T,H,E,K", [(8, 128, 7168, 288, 8), (2, 64, 2048, 16, 4)])
+def test_self_describing_payloads_group(R, T, H, E, K, use_fp8):
+    bufs = local_group(R, Buffer.get_ep_buffer_size_hint(T, H, R, E))
+    _check_layer(R, T, H, E, K, use_fp8, bufs, seed=1)
+    assert all(b.runtime.status() == 0 for b in bufs)
+
+
+@pytest.mark.parametrize("use_fp8", [False, True])
+def test_self_describing_payloads_single_rank(use_fp8):
+    T, H, E, K = 128, 7168, 288, 8
+    buf = Buffer(FakeGroup(0, 1), Buffer.get_ep_buffer_size_hint(T, H, 1, E))
+    _check_layer(1, T, H, E, K, use_fp8, [buf], seed=2)
+    assert buf.runtime.status() == 0
