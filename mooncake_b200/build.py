@@ -8,7 +8,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-LIB = os.path.join(HERE, "libmcep.so")
+# MCEP_LIB points the package at a library built elsewhere (e.g. a diagnostic build)
+LIB = os.environ.get("MCEP_LIB") or os.path.join(HERE, "libmcep.so")
 SOURCES = ["ep_kernels.cu", "ep_runtime.cu", "ep_noalloc.cu"]
 HEADERS = ["ep_kernels.cuh", "ep_device.cuh", os.path.join("..", "..", "include", "mcep.h")]
 
@@ -31,6 +32,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "-gencode", "arch=compute_100a,code=sm_100a",
            "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",
            "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+    cmd[1:1] = os.environ.get("MCEP_NVCC_FLAGS", "").split()  # e.g. -DMCEP_PHASE_TRACE
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

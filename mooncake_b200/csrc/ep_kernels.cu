@@ -230,6 +230,32 @@ __device__ __forceinline__ uint32_t resolve_flag(const WaitSpec& w, int i, int s
 }
 
 // =============================================================================
+// phase trace (diagnostic builds only: -DMCEP_PHASE_TRACE)
+// =============================================================================
+// Thread 0 of every block stamps the SM cycle counter at the phase boundaries
+// of the four bodies below (slot 0 also takes the global timer, so blocks can
+// be lined up against each other). Compiled out of the normal library.
+#ifdef MCEP_PHASE_TRACE
+constexpr int kTraceBodies = 4, kTraceBlocks = 1024, kTraceSlots = 8;
+__device__ unsigned long long g_phase_trace[kTraceBodies][kTraceBlocks][kTraceSlots];
+#define MCEP_TRACE(body, slot)                                                     \
+    do {                                                                           \
+        if (threadIdx.x == 0 && blockIdx.x < kTraceBlocks) {                       \
+            g_phase_trace[body][blockIdx.x][slot] = (unsigned long long)clock64(); \
+            if ((slot) == 0) g_phase_trace[body][blockIdx.x][kTraceSlots - 1] = globaltimer_ns(); \
+        }                                                                          \
+    } while (0)
+#define MCEP_TRACE_SYNC() __syncthreads()
+#else
+#define MCEP_TRACE(body, slot) \
+    do {                       \
+    } while (0)
+#define MCEP_TRACE_SYNC() \
+    do {                  \
+    } while (0)
+#endif
+
+// =============================================================================
 // routing layout
 // =============================================================================
 // One block owns `epc` consecutive experts. It builds, in shared memory, one
@@ -391,6 +417,7 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
 
     pdl_wait();
     pdl_launch_dependents();
+    MCEP_TRACE(0, 0);
     // everything the block needs from memory is requested before the first
     // barrier, so the routing work costs one memory round trip, not several
     if (kFused)
@@ -403,8 +430,9 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
         }
     }
     // The tables above are read by other threads further down. The token loop
-    // has barriers of its own, but a block without tokens skips it.
-    __syncthreads();
+    // has barriers of its own before any such read (and its first loads should
+    // not wait for this prologue), but a block without tokens skips the loop.
+    if ((int)blockIdx.x >= p.T) __syncthreads();
 
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
         const char* xrow = xb + (size_t)t * p.H * 2;
@@ -416,9 +444,17 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
         const int tpw = 32 / p.K;            // tokens per warp pass (K <= 16)
         const int sk = lane % p.K, st = lane / p.K;
         const bool lane_used = st < tpw;
-        int e_first = -1;
-        if (scan_now && lane_used && warp * tpw + st < p.T)
-            e_first = (int)__ldg(p.topk_idx + (size_t)(warp * tpw + st) * p.K + sk);
+        // the first kScanAhead passes of the scan are requested here, together
+        // with the row, so the scan does not pay a memory round trip per pass
+        constexpr int kScanAhead = 4;
+        int e_ahead[kScanAhead];
+#pragma unroll
+        for (int u = 0; u < kScanAhead; ++u) {
+            const int t2 = (warp + u * nwarps) * tpw + st;
+            e_ahead[u] = -1;
+            if (scan_now && lane_used && t2 < p.T)
+                e_ahead[u] = (int)__ldg(p.topk_idx + (size_t)t2 * p.K + sk);
+        }
         int my_slot = -1;
         if (tid < kMaxTopk) {
             int e = tid < p.K ? (int)__ldg(p.topk_idx + (size_t)t * p.K + tid) : -1;
@@ -440,11 +476,9 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
             // histogram, and for this block's token the number of earlier tokens
             // per chosen expert. A repeated expert inside a token is counted once
             // (lanes holding the same (token, expert) elect the lowest lane).
-            for (int base = warp * tpw; base < p.T; base += nwarps * tpw) {
+            auto count_pass = [&](int base, int e) {
                 const int t2 = base + st;
                 const bool valid = lane_used && t2 < p.T;
-                int e = (base == warp * tpw) ? e_first
-                                             : (valid ? (int)__ldg(p.topk_idx + (size_t)t2 * p.K + sk) : -1);
                 if (!valid || e >= p.E) e = -1;
                 const unsigned key = e >= 0 ? (((unsigned)st << 16) | (unsigned)e) : (0x80000000u | lane);
                 const unsigned grp = __match_any_sync(kFull, key);
@@ -455,6 +489,16 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
                         if (kk >= 0) atomicAdd(&s_before[kk], 1);
                     }
                 }
+            };
+#pragma unroll
+            for (int u = 0; u < kScanAhead; ++u) {
+                const int base = (warp + u * nwarps) * tpw;
+                if (base < p.T) count_pass(base, e_ahead[u]);
+            }
+            for (int base = (warp + kScanAhead * nwarps) * tpw; base < p.T; base += nwarps * tpw) {
+                const int t2 = base + st;
+                count_pass(base, (lane_used && t2 < p.T) ? (int)__ldg(p.topk_idx + (size_t)t2 * p.K + sk)
+                                                         : -1);
             }
             __syncthreads();
         }
@@ -482,6 +526,7 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
             s_slot[tid] = s;
         }
         __syncthreads();
+        if (t == (int)blockIdx.x) MCEP_TRACE(0, 1);  // routing of the first token is known
 
         for (int tile = warp; tile < ntiles; tile += nwarps) {
             const int c = tile * 32 + lane;
@@ -539,6 +584,7 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
         __syncthreads();
     }
 
+    MCEP_TRACE(0, 2);  // all payload stores are issued
     // per-expert duties, spread over the grid: the receive layout of a single
     // rank, or the flag of an expert this rank sends nothing to
     for (int e = blockIdx.x * nthr + tid; e < p.E; e += gridDim.x * nthr) {
@@ -564,7 +610,9 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
         // counter, observed every contributor's fence: all of that expert's
         // messages are performed system-wide, and the flag may follow with only
         // a device-scope fence in between.
+        MCEP_TRACE(0, 3);
         if (tid == 0) __threadfence_system();
+        MCEP_TRACE(0, 4);  // the fence has returned
         __syncthreads();
         for (int e = tid; e < p.E; e += nthr) {
             const int c = cta_cnt[e];
@@ -581,6 +629,7 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
             }
         }
     }
+    MCEP_TRACE(0, 5);
 }
 
 // =============================================================================
@@ -608,11 +657,13 @@ __device__ __forceinline__ void dispatch_recv_body(const DispatchRecvParams& p, 
     const int S = p.H / 128;
     pdl_wait();
     pdl_launch_dependents();
+    MCEP_TRACE(1, 0);
     for (int i = tid; i < n; i += nthr) {
         const uint32_t v = resolve_flag(p.w, i, i % p.R, (i % gridDim.x) == blockIdx.x);
         pre[i] = v ? (int)v - 1 : 0;
     }
     __syncthreads();
+    MCEP_TRACE(1, 1);  // every flag has a verdict
     for (int le = tid; le < p.L; le += nthr) {
         int run = 0;
         for (int src = 0; src < p.R; ++src) {
@@ -626,9 +677,13 @@ __device__ __forceinline__ void dispatch_recv_body(const DispatchRecvParams& p, 
     }
     __syncthreads();
     block_exclusive_scan(pre, n, s_wt);
+    MCEP_TRACE(1, 2);  // layout done
     const int total = pre[n];
     const int nwarps = nthr >> 5;
-    for (int g = blockIdx.x * nwarps + warp; g < total; g += gridDim.x * nwarps) {
+    // rows are dealt to the blocks one at a time (warp w of block b takes row
+    // w * grid + b, ...): a batch with fewer rows than the grid has warps still
+    // spreads over every SM
+    for (int g = warp * gridDim.x + blockIdx.x; g < total; g += gridDim.x * nwarps) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R;
         const int j = g - pre[i];
@@ -685,6 +740,8 @@ __device__ __forceinline__ void dispatch_recv_body(const DispatchRecvParams& p, 
         }
         if (lane == 0) p.recv_src_info[out_row] = tok;
     }
+    MCEP_TRACE_SYNC();
+    MCEP_TRACE(1, 3);
 }
 
 // =============================================================================
@@ -712,6 +769,7 @@ __device__ __forceinline__ void combine_send_body(const CombineSendParams& p, in
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
     pdl_wait();
     pdl_launch_dependents();
+    MCEP_TRACE(2, 0);
     for (int i = tid; i < n; i += nthr) {
         pre[i] = (int)(__ldg(p.layout_range + i) & 0xffffffffll);
         cta_cnt[i] = 0;
@@ -733,11 +791,13 @@ __device__ __forceinline__ void combine_send_body(const CombineSendParams& p, in
     }
     __syncthreads();
     block_exclusive_scan(pre, n, s_wt);
+    MCEP_TRACE(2, 1);  // layout read and scanned
     const int total = pre[n];
     const char* xb = reinterpret_cast<const char*>(p.x);
     constexpr int kB = 8;  // 8 x 32 B per lane in flight: a 7168-wide row takes two round trips
     const int nwarps = nthr >> 5;
-    for (int g = blockIdx.x * nwarps + warp; g < total; g += gridDim.x * nwarps) {
+    // rows dealt to the blocks one at a time, as in the dispatch receive phase
+    for (int g = warp * gridDim.x + blockIdx.x; g < total; g += gridDim.x * nwarps) {
         const int i = find_segment(pre, n, g);
         const int le = i / p.R, d = i - le * p.R;
         const int j = g - pre[i];
@@ -780,7 +840,9 @@ __device__ __forceinline__ void combine_send_body(const CombineSendParams& p, in
         if (lane == 0) atomicAdd(&cta_cnt[i], 1);
     }
     __syncthreads();
+    MCEP_TRACE(2, 2);  // all rows are issued
     if (tid == 0) __threadfence_system();
+    MCEP_TRACE(2, 3);  // the fence has returned
     __syncthreads();
     for (int i = tid; i < n; i += nthr) {
         const int c = cta_cnt[i];
@@ -797,6 +859,7 @@ __device__ __forceinline__ void combine_send_body(const CombineSendParams& p, in
             }
         }
     }
+    MCEP_TRACE(2, 4);
 }
 
 // Single rank: rowmap[t][k] = packed row of (token t, expert topk[t][k]) as the
@@ -845,6 +908,7 @@ __device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p
     const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
     pdl_wait();
     pdl_launch_dependents();
+    MCEP_TRACE(3, 0);
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
         int e = -1, r = 0;
         float w = 0.f;
@@ -898,6 +962,7 @@ __device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p
             s_w[tid] = w;
         }
         __syncthreads();
+        if (t == (int)blockIdx.x) MCEP_TRACE(3, 1);  // the first token's rows are located / have arrived
         for (int tile = warp; tile < ntiles; tile += nwarps) {
             const int c = tile * 32 + lane;
             if (c >= nchunks) continue;
@@ -921,6 +986,8 @@ __device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p
                  pack_bf16x16(acc));
         }
     }
+    MCEP_TRACE_SYNC();
+    MCEP_TRACE(3, 2);
 }
 
 // =============================================================================
@@ -1140,3 +1207,13 @@ cudaError_t launch_combine_reduce(const CombineReduceParams& p, const LaunchCtx&
 }
 
 }  // namespace mcep
+
+#ifdef MCEP_PHASE_TRACE
+// Diagnostic builds only: copies the trace of the calling thread's device out
+// ([body 4][block 1024][slot 8] u64) after waiting for the device to go idle.
+extern "C" int mcep_debug_read_phase_trace(unsigned long long* out, size_t bytes) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (bytes > sizeof(mcep::kernels::g_phase_trace)) bytes = sizeof(mcep::kernels::g_phase_trace);
+    return cudaMemcpyFromSymbol(out, mcep::kernels::g_phase_trace, bytes) == cudaSuccess ? 0 : -1;
+}
+#endif
