@@ -897,7 +897,9 @@ __global__ void __launch_bounds__(256) ep_combine_invert_kernel(CombineInvertPar
 // One block per token, one warp per 512-channel tile; each lane owns 16
 // channels: up to K 32-byte loads in flight, fp32 FMA accumulation in k order,
 // one bf16 rounding, one 32-byte store (mooncake_ep_kernel.cu:715-752).
-template <bool kDirect>
+// kDepth rows are requested before the first of them is used: 8 when there is
+// one block per SM anyway (small batches), 4 when several blocks share an SM.
+template <bool kDirect, int kDepth>
 __device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p) {
     __shared__ const char* s_ptr[kMaxTopk];
     __shared__ float s_w[kMaxTopk];
@@ -969,17 +971,25 @@ __device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p
             float acc[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-#pragma unroll 4
-            for (int k = 0; k < p.K; ++k) {
-                const char* rp = s_ptr[k];
-                if (rp == nullptr) continue;
-                const V32 v = kDirect ? ld32_readonly(rp + (size_t)c * 32)
-                                      : ld32_coherent(rp + (size_t)c * 32);
-                const float wk = s_w[k];
+            // s_ptr has kMaxTopk entries, null from K on
+            for (int k0 = 0; k0 < p.K; k0 += kDepth) {
+                V32 v[kDepth];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    acc[2 * i] = fmaf(bf16lo(v.w[i]), wk, acc[2 * i]);
-                    acc[2 * i + 1] = fmaf(bf16hi(v.w[i]), wk, acc[2 * i + 1]);
+                for (int b = 0; b < kDepth; ++b) {
+                    const char* rp = s_ptr[k0 + b];
+                    if (rp != nullptr)
+                        v[b] = kDirect ? ld32_readonly(rp + (size_t)c * 32)
+                                       : ld32_coherent(rp + (size_t)c * 32);
+                }
+#pragma unroll
+                for (int b = 0; b < kDepth; ++b) {
+                    if (s_ptr[k0 + b] == nullptr) continue;
+                    const float wk = s_w[k0 + b];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        acc[2 * i] = fmaf(bf16lo(v[b].w[i]), wk, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(bf16hi(v[b].w[i]), wk, acc[2 * i + 1]);
+                    }
                 }
             }
             st32(reinterpret_cast<char*>(p.combined_x) + ((size_t)t * p.H + (size_t)c * 16) * 2,
@@ -1025,16 +1035,17 @@ __global__ void __launch_bounds__(kRowWarps * 32) ep_combine_send_kernel(Combine
     combine_send_body(p, smem_i32);
 }
 
-template <bool kDirect>
+template <bool kDirect, int kDepth>
 __global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReduceParams p) {
-    combine_reduce_body<kDirect>(p);
+    static_assert(kMaxTopk % kDepth == 0, "the row batches must tile the top-k table");
+    combine_reduce_body<kDirect, kDepth>(p);
 }
 
 __global__ void __launch_bounds__(512) ep_combine_kernel(CombineSendParams sp, CombineReduceParams rp) {
     extern __shared__ int smem_i32[];
     combine_send_body(sp, smem_i32);
     __syncthreads();
-    combine_reduce_body<false>(rp);
+    combine_reduce_body<false, 8>(rp);
 }
 
 // threads per block: one warp per tile, at most 16 warps
@@ -1200,7 +1211,9 @@ cudaError_t launch_combine_invert(const CombineInvertParams& p, const LaunchCtx&
 
 cudaError_t launch_combine_reduce(const CombineReduceParams& p, const LaunchCtx& ctx) {
     const int threads = block_threads(p.H);
-    auto k = p.direct ? ep_combine_reduce_kernel<true> : ep_combine_reduce_kernel<false>;
+    const bool deep = p.T <= ctx.num_sms;  // one block per SM at most: spend registers on loads in flight
+    auto k = p.direct ? (deep ? ep_combine_reduce_kernel<true, 8> : ep_combine_reduce_kernel<true, 4>)
+                      : (deep ? ep_combine_reduce_kernel<false, 8> : ep_combine_reduce_kernel<false, 4>);
     const int grid = persistent_grid(p.T, k, threads, 0, ctx);
     return launch(p.direct ? "ep_combine_reduce_direct" : "ep_combine_reduce", k, dim3(grid),
                   dim3(threads), 0, ctx, p);
