@@ -169,19 +169,20 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------
 # CPU legs (the oracle port of the reference's torch path)
 # ----------------------------------------------------------------------------------------
-def cpu_layer_seconds(w, R, budget_s, min_iters=2, max_iters=50):
+def cpu_layer_seconds(w, R, budget_s, warmup=1, steps=50):
     """Times dispatch+combine of all R ranks with the CPU restatement of the
-    reference's torch path (same arithmetic: amax/448 scales, bf16 running sum).
-    Returns (seconds per layer, iterations run)."""
+    reference's torch path (same arithmetic: amax/448 scales, bf16 running sum):
+    `warmup` untimed layers, then `steps` timed ones. The time budget can cut
+    both short (at least one of each runs). Returns (seconds per layer, timed
+    layers run, warm-up layers run)."""
     import torch
     from oracle import ep_oracle as ora
     T, H, E, K = w["T"], w["H"], w["E"], w["K"]
     ins = [make_inputs(w, r) for r in range(R)]
     xs, idxs, ws = [i[0] for i in ins], [i[1] for i in ins], [i[2] for i in ins]
     L = E // R
-    times = []
-    t_start = time.perf_counter()
-    while len(times) < max_iters:
+
+    def layer():
         t0 = time.perf_counter()
         res = ora.dispatch(xs, idxs, T, E, w["fp8"], arith="fallback")
         t1 = time.perf_counter()
@@ -195,11 +196,21 @@ def cpu_layer_seconds(w, R, budget_s, min_iters=2, max_iters=50):
         t2 = time.perf_counter()
         ora.combine(ys, idxs, ws, res, T, E, arith="fallback")
         t3 = time.perf_counter()
-        times.append((t1 - t0) + (t3 - t2))
-        if len(times) >= min_iters and time.perf_counter() - t_start > budget_s:
+        return (t1 - t0) + (t3 - t2)
+
+    t_start = time.perf_counter()
+    warm = 0
+    while warm < max(1, warmup):
+        layer()
+        warm += 1
+        if time.perf_counter() - t_start > budget_s / 4:
             break
-    times = times[1:] if len(times) > 1 else times  # first iteration warms caches
-    return sum(times) / len(times), len(times)
+    times = []
+    while len(times) < max(1, steps):
+        times.append(layer())
+        if time.perf_counter() - t_start > budget_s:
+            break
+    return sum(times) / len(times), len(times), warm
 
 
 def run_reference_arm(args):
@@ -212,13 +223,11 @@ def run_reference_arm(args):
     R = args.gpus
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    budget = 150.0
-    sec, iters = cpu_layer_seconds(w, R, budget_s=budget, min_iters=max(2, min(args.warmup, 2)),
-                                   max_iters=max(2, args.steps + 1))
+    sec, iters, warm = cpu_layer_seconds(w, R, budget_s=150.0, warmup=args.warmup, steps=args.steps)
     value = w["T"] * R / sec
     line = {
         "impl": "reference", "metric": "ep_dispatch_combine_tokens_per_s", "value": value,
-        "unit": "tokens/s", "n_gpus": R, "steps": iters, "warmup": 1,
+        "unit": "tokens/s", "n_gpus": R, "steps": iters, "warmup": warm,
         "ms_per_step": sec * 1e3, "us_per_layer": sec * 1e6, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3+bf16" if w["fp8"] else "bf16",
         "data": "synthetic",
@@ -492,7 +501,7 @@ def run_ours(args):
     cpu_baseline = None
     if R == 1 and not args.no_cpu_baseline:
         torch.set_num_threads(max(1, (os.cpu_count() or 1)))
-        sec, iters = cpu_layer_seconds(w, 1, budget_s=12.0)
+        sec, iters, _ = cpu_layer_seconds(w, 1, budget_s=12.0)
         cpu_baseline = {"value": T / sec, "unit": "tokens/s", "cores": torch.get_num_threads(),
                         "kind": "port",
                         "sample": f"{iters} dispatch+combine layers of this workload at 1 rank "

@@ -82,18 +82,20 @@ int mcep_buffer_destroy(mcep_buffer* buf);
 int mcep_buffer_ibgda_disabled(const mcep_buffer* buf);
 int mcep_buffer_p2p_enabled(const mcep_buffer* buf);
 int mcep_buffer_is_roce(const mcep_buffer* buf);
-/* 1 when every active rank's memory is mapped (single rank: always 1). */
+/* 1 when every active rank's memory is mapped (single rank: always 1);
+ * mooncake-ep/include/mooncake_ep_buffer.h:143, `use_fast_path`. */
 int mcep_buffer_use_fast_path(const mcep_buffer* buf);
 
-/* MooncakeEpBuffer::get_ipc_handle (mooncake_ep_buffer.cpp:518-521):
+/* MooncakeEpBuffer::get_ipc_handle (mooncake-ep/src/mooncake_ep_buffer.cpp:518-521):
  * writes MCEP_IPC_HANDLE_INT32S int32 to `out` (capacity in int32),
  * `*n_written` = 0 when P2P is disabled. */
 int mcep_buffer_get_ipc_handle(mcep_buffer* buf, int32_t* out, int capacity,
                                int* n_written);
 
-/* MooncakeEpBuffer::sync_nvlink_ipc_handles (mooncake_ep_buffer.cpp:523-529)
- * and P2pDeviceTransportImpl::importPeerHandles
- * (p2p_device_transport.cpp:491-715). `handles` is [num_ranks][n_per_handle]
+/* MooncakeEpBuffer::sync_nvlink_ipc_handles
+ * (mooncake-ep/src/mooncake_ep_buffer.cpp:523-529) and
+ * P2pDeviceTransportImpl::importPeerHandles
+ * (mooncake-transfer-engine/src/transport/device/p2p_device_transport.cpp:491-715). `handles` is [num_ranks][n_per_handle]
  * int32, `active_ranks_mask` is [num_ranks] (0 = do not map that rank). A later
  * call replaces the earlier mapping (membership refresh). */
 int mcep_buffer_sync_nvlink_ipc_handles(mcep_buffer* buf,
@@ -108,14 +110,23 @@ int mcep_buffer_local_base(mcep_buffer* buf, void** base);
 int mcep_buffer_set_peer_bases(mcep_buffer* buf, void* const* bases,
                                const int32_t* available);
 
-/* Options: "force_staged" (1 = a single rank also goes through the symmetric
- * staging buffers and flags, as multi-rank groups do),
- * "hard_timeout_ms" (upper bound applied to every device-side wait, also when
- * timeout_us is -1; default 10000). */
+/* Options (no counterpart in the reference):
+ *   "force_staged"    1 = a single rank also goes through the symmetric staging
+ *                     buffers and flags, as multi-rank groups do (default 0)
+ *   "hard_timeout_ms" upper bound applied to every device-side wait, also when
+ *                     timeout_us is -1 (default 10000)
+ *   "pdl"             1 = kernels of one call are chained with programmatic
+ *                     dependent launch (default 1)
+ *   "fuse_layout"     1 = small batches count their routing layout inside the
+ *                     send kernel instead of in a kernel of its own (default 1)
+ *   "one_kernel"      1 = small batches in a group run the send and the receive
+ *                     phase of a call in one launch (default 1)
+ * An unknown name is an error. */
 int mcep_buffer_set_option(mcep_buffer* buf, const char* name, int64_t value);
 
 /* Copies up to `n` int32 status words (0 = clean). Word 0: bit mask of
- * anomalies (1 slot out of range, 2 hard wait bound hit, 4 bad source index). */
+ * anomalies (1 slot out of range, 2 hard wait bound hit, 4 bad source index).
+ * No counterpart in the reference, whose kernels trap instead. */
 int mcep_buffer_status(mcep_buffer* buf, int32_t* out, int n);
 
 /* ---- dispatch --------------------------------------------------------------

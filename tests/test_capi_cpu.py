@@ -80,3 +80,60 @@ def test_zero_copy_is_rejected_like_the_reference():
         b.get_next_combine_buffer(None)
     with pytest.raises(NotImplementedError):
         b.combine(None, None, None, None, 0, (), zero_copy=True)
+
+
+_C_KINDS = {"int32_t": ("i", 4), "int64_t": ("i", 8), "uint64_t": ("u", 8)}
+
+
+def _header_struct(name):
+    """[(field, size in bytes)] of a struct in include/mcep.h, in declaration order."""
+    text = open(os.path.join(ROOT, "include", "mcep.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), text, flags=re.S).group(1)
+    out = []
+    for decl in [d.strip() for d in body.split(";") if d.strip()]:
+        m = re.match(r"(const\s+)?(\w+)\s*(\*?)\s*(\w+)$", decl)
+        assert m, decl
+        ctype, ptr, field = m.group(2), m.group(3), m.group(4)
+        out.append((field, 8 if ptr else _C_KINDS[ctype][1]))
+    return out
+
+
+@pytest.mark.parametrize("cname,pyname", [("mcep_dispatch_args", "_DispatchArgs"),
+                                          ("mcep_combine_args", "_CombineArgs")])
+def test_argument_structs_match_the_header(cname, pyname, tmp_path):
+    """The ctypes mirror has the header's fields in the header's order, and the
+    offsets a C compiler gives them."""
+    from mooncake_b200 import ep
+    py = getattr(ep, pyname)
+    want = _header_struct(cname)
+    got = [(n, ctypes.sizeof(t)) for n, t in py._fields_]
+    assert got == want
+    src = tmp_path / "offsets.c"
+    lines = "\n".join(f'    printf("%zu\\n", offsetof({cname}, {n}));' for n, _ in want)
+    src.write_text('#include <stddef.h>\n#include <stdio.h>\n#include "mcep.h"\n'
+                   f'int main(void) {{\n{lines}\n    printf("%zu\\n", sizeof({cname}));\n    return 0;\n}}\n')
+    exe = tmp_path / "offsets"
+    import subprocess
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src)], check=True)
+    nums = [int(v) for v in subprocess.run([str(exe)], check=True, capture_output=True,
+                                           text=True).stdout.split()]
+    assert nums[:-1] == [getattr(py, n).offset for n, _ in want]
+    assert nums[-1] == ctypes.sizeof(py)
+
+
+def test_every_entry_point_cites_what_it_replaces():
+    """Each declaration in the header is preceded by a comment that names the
+    reference interface it stands in for, or says that there is none."""
+    text = open(os.path.join(ROOT, "include", "mcep.h")).read()
+    for name in _declared_functions():
+        pos = re.search(r"\b%s\s*\(" % name, re.sub(r"/\*.*?\*/", lambda m: " " * len(m.group(0)),
+                                                    text, flags=re.S)).start()
+        before = text[:pos]
+        # the nearest section or declaration comment above the declaration
+        # (field comments inside the argument structs are short: skip them)
+        comments = [c for c in re.findall(r"/\*.*?\*/", before, flags=re.S) if len(c) > 70]
+        assert comments, name
+        near = " ".join(comments[-3:])
+        assert re.search(r"mooncake-[a-z-]+/|no counterpart|No counterpart|not in the reference|"
+                         r"Measurement aid|last failure|has launched", near), name
