@@ -239,6 +239,10 @@ int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int
 
 int mcep_buffer_destroy(mcep_buffer* b) {
     if (b == nullptr) return MCEP_OK;
+    // the caller may have moved to another device since the buffer was created
+    int cur = b->device;
+    cudaGetDevice(&cur);
+    if (cur != b->device) cudaSetDevice(b->device);
     cudaDeviceSynchronize();
     for (void* p : b->ipc_opened) cudaIpcCloseMemHandle(p);
     if (b->base) cudaFree(b->base);
@@ -247,6 +251,7 @@ int mcep_buffer_destroy(mcep_buffer* b) {
     if (b->ev_a) cudaEventDestroy(b->ev_a);
     if (b->ev_b) cudaEventDestroy(b->ev_b);
     if (b->comm_stream) cudaStreamDestroy(b->comm_stream);
+    if (cur != b->device) cudaSetDevice(cur);
     cudaGetLastError();
     delete b;
     return MCEP_OK;
