@@ -103,16 +103,40 @@ int mcep_buffer_sync_nvlink_ipc_handles(mcep_buffer* buf,
                                         int n_per_handle,
                                         const int32_t* active_ranks_mask);
 
+/* Membership refresh. The words ranks exchange carry the number of the call
+ * they belong to, so all ranks of a group must have made the same number of
+ * dispatch and of combine calls. get_ipc_handle leaves this rank's two call
+ * counters in its symmetric memory; sync_nvlink_ipc_handles reads those of
+ * every rank it maps and continues from the largest. A rank that sat out some
+ * calls (masked out) or was re-created from scratch is therefore back in step
+ * after every rank has run the two calls (Buffer.update_ep_member in the
+ * reference's wrapper, mooncake-wheel/mooncake/mooncake_ep_buffer.py:306-307),
+ * with nothing in flight. Handles of dispatch calls made before a counter
+ * jumped can no longer be combined. */
+
 /* In-process groups (several logical ranks in one process, e.g. tests that run
  * the ranks one after the other on one GPU): hand the peers' base pointers over
- * directly instead of through IPC handles. No counterpart in the reference. */
+ * directly instead of through IPC handles (local_base plays the part of
+ * get_ipc_handle, set_peer_bases that of sync_nvlink_ipc_handles). No
+ * counterpart in the reference. */
 int mcep_buffer_local_base(mcep_buffer* buf, void** base);
 int mcep_buffer_set_peer_bases(mcep_buffer* buf, void* const* bases,
                                const int32_t* available);
+/* In a group the kernels of different ranks wait for one another (an expert's
+ * owner answers every source), which is fine on GPUs of their own but not as
+ * separate launches on ONE GPU: nothing would make them run at the same time.
+ * With option "defer_launch" = 1 a buffer's mcep_dispatch / mcep_combine call
+ * prepares everything and launches nothing; mcep_launch_deferred then starts
+ * what the listed buffers have prepared - all dispatch or all combine calls of
+ * the same kind, same stream - as ONE cooperative launch that carries every
+ * rank. (A combine call in hook mode needs no deferral: its first phase waits
+ * for nobody.) Tests and single-GPU experiments only; no counterpart in the
+ * reference. */
+int mcep_launch_deferred(mcep_buffer* const* bufs, int n);
 
 /* Options (no counterpart in the reference):
- *   "force_staged"    1 = a single rank also goes through the symmetric staging
- *                     buffers and flags, as multi-rank groups do (default 0)
+ *   "force_staged"    1 = a single rank also goes through symmetric memory and
+ *                     the word exchange, as multi-rank groups do (default 0)
  *   "hard_timeout_ms" upper bound applied to every device-side wait, also when
  *                     timeout_us is -1 (default 10000)
  *   "pdl"             1 = kernels of one call are chained with programmatic
@@ -121,13 +145,46 @@ int mcep_buffer_set_peer_bases(mcep_buffer* buf, void* const* bases,
  *                     send kernel instead of in a kernel of its own (default 1)
  *   "one_kernel"      1 = small batches in a group run the send and the receive
  *                     phase of a call in one launch (default 1)
+ *   "defer_launch"    1 = in-process groups: prepare calls, launch them together
+ *                     with mcep_launch_deferred (default 0)
  * An unknown name is an error. */
 int mcep_buffer_set_option(mcep_buffer* buf, const char* name, int64_t value);
 
 /* Copies up to `n` int32 status words (0 = clean). Word 0: bit mask of
- * anomalies (1 slot out of range, 2 hard wait bound hit, 4 bad source index).
+ * anomalies (1 row or slot out of range, 2 hard wait bound hit, 4 bad source
+ * index, 8 a rank marked active has no mapped buffer and was left alone).
  * No counterpart in the reference, whose kernels trap instead. */
 int mcep_buffer_status(mcep_buffer* buf, int32_t* out, int n);
+
+/* Dispatch and combine calls this buffer has made (or adopted at a membership
+ * refresh). No counterpart in the reference. */
+int mcep_buffer_call_counts(const mcep_buffer* buf, uint32_t* dispatch_calls,
+                            uint32_t* combine_calls);
+
+/* Where the NEXT dispatch call of this buffer lands its rows: the packed
+ * receive tensor [E/R][R*M][H] (e4m3 bytes or bf16) inside symmetric memory,
+ * for the given shape. A binding that passes this pointer as
+ * `packed_recv_x` gets the rows in place - peers store them there directly -
+ * and the call moves no payload on the receiving side; the memory is reused by
+ * the dispatch call after the next one. With any other pointer the rows are
+ * copied out into it, as the reference does
+ * (mooncake-ep/src/mooncake_ep_kernel.cu:442-466). `*out` is NULL for a single
+ * rank (it writes the caller's tensor directly) or when the buffer is too small
+ * for the shape (the dispatch call then reports it). */
+int mcep_buffer_next_recv_x(mcep_buffer* buf, int num_max_dispatch_tokens_per_rank,
+                            int hidden, int num_experts, int use_fp8, void** out,
+                            size_t* bytes);
+
+/* Zero-copy combine: the tensor [E/R][R*M][H] bf16 inside symmetric memory that
+ * the NEXT combine call reads when it is given `zero_copy = 1`; the caller's
+ * expert kernels write their outputs there instead of into a tensor of their
+ * own (docs/source/design/mooncake-ep.md:165-167 in the Mooncake tree; the
+ * reference's wrapper rejects it today, mooncake-wheel/mooncake/
+ * mooncake_ep_buffer.py:551,680). `*out` is NULL for a single rank, whose
+ * combine reads the caller's tensor directly either way. */
+int mcep_buffer_next_combine_buffer(mcep_buffer* buf, int num_max_dispatch_tokens_per_rank,
+                                    int hidden, int num_experts, void** out,
+                                    size_t* bytes);
 
 /* ---- dispatch --------------------------------------------------------------
  * Replaces MooncakeEpBuffer::dispatch
@@ -141,6 +198,10 @@ int mcep_buffer_status(mcep_buffer* buf, int32_t* out, int n);
  *   packed_recv_layout_range [E/R][R] int64    (begin << 32) | count, 0 if empty
  * Rows are ordered by source rank, then by token index. `active_ranks` [R]
  * int32 is read AND written (a source that misses `timeout_us` is set to 0).
+ * In a group the owner of an expert fixes the layout from the counts all sources
+ * announce and tells each source where its rows go; if a source goes silent
+ * after announcing its counts, its rows stay in the layout with unspecified
+ * contents and the source is marked inactive.
  */
 typedef struct mcep_dispatch_args {
     const void* x;              /* [num_tokens][hidden] bf16 */
@@ -176,6 +237,11 @@ int mcep_dispatch(mcep_buffer* buf, const mcep_dispatch_args* args,
  *   combined_x   [num_combined_tokens][H] bf16
  * combined[t] = bf16( sum over k in order, fp32 FMA, of w[t][k] * x_row ),
  * skipping topk_idx < 0 and experts whose owner rank is inactive.
+ * In a group, `src_info` must be the tensor a dispatch call of this buffer
+ * filled, and that call must be one of the buffer's last two dispatch calls
+ * (the rows' positions at the experts' owners are kept from then); the same
+ * handle may be combined more than once. With `zero_copy` the expert outputs
+ * are read from mcep_buffer_next_combine_buffer's tensor and `x` is ignored.
  */
 typedef struct mcep_combine_args {
     const void* x;
@@ -191,7 +257,7 @@ typedef struct mcep_combine_args {
     int32_t num_max_dispatch_tokens_per_rank;
     int32_t num_experts;
     int64_t timeout_us;
-    int32_t zero_copy;          /* must be 0 */
+    int32_t zero_copy;          /* read mcep_buffer_next_combine_buffer's tensor instead of x */
     void* combined_x;
     int32_t async_finish;
     int32_t return_recv_hook;
@@ -260,6 +326,12 @@ int mcep_combine_single_rank_static(const void* x, const int64_t* topk_idx,
                                     int num_max_dispatch_tokens_per_rank,
                                     void* combined_x, uint64_t stream);
 const char* mcep_static_last_error(void);
+/* No counterpart in the reference. Anomalies the kernels of
+ * mcep_combine_single_rank_static met in the handle they were given (bit mask
+ * as in mcep_buffer_status: 1 row out of range, 4 bad token index) since the
+ * last call of this function on the current device; reading clears the word.
+ * Waits for the device to go idle first; allocates nothing. */
+int mcep_static_status(int32_t* out);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,8 @@
 """Builds libmcep.so (the CUDA kernels and the C ABI) in-tree with nvcc, for sm_100a only."""
 from __future__ import annotations
 
+import fcntl
+import hashlib
 import os
 import shutil
 import subprocess
@@ -14,19 +16,51 @@ SOURCES = ["ep_kernels.cu", "ep_runtime.cu", "ep_noalloc.cu"]
 HEADERS = ["ep_kernels.cuh", "ep_device.cuh", os.path.join("..", "..", "include", "mcep.h")]
 
 
+STAMP = LIB + ".sources"  # digest of the sources the library was built from
+
+
+def _digest() -> str:
+    h = hashlib.sha256()
+    h.update(os.environ.get("MCEP_NVCC_FLAGS", "").encode())
+    for f in SOURCES + HEADERS:
+        path = os.path.join(CSRC, f)
+        if os.path.exists(path):
+            with open(path, "rb") as fh:
+                h.update(fh.read())
+    return h.hexdigest()
+
+
 def _stale() -> bool:
+    """True when the library is missing or was built from other sources (file
+    contents are compared, not times: a copy of the tree keeps no times)."""
     if not os.path.exists(LIB):
         return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
-    return any(os.path.getmtime(d) > t for d in deps)
+    try:
+        with open(STAMP) as fh:
+            return fh.read().strip() != _digest()
+    except OSError:
+        return True
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB
+    # several processes of one job may import the package at once: one builds
+    with open(LIB + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _stale():
+                return LIB
+            return _build_locked(force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool) -> str:
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
+        if os.path.exists(LIB) and not force:
+            return LIB  # a prebuilt library and no compiler: use what is there
         raise RuntimeError("mooncake_b200: nvcc not found; cannot build libmcep.so")
     cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo",
            "-gencode", "arch=compute_100a,code=sm_100a",
@@ -37,6 +71,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
     subprocess.run(cmd, check=True)
+    with open(STAMP, "w") as fh:
+        fh.write(_digest())
     return LIB
 
 

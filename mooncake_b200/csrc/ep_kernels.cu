@@ -1,20 +1,30 @@
-// Hand-written sm_100a kernels of the EP hot path: routing layout, dispatch
-// (send / wait / pack) and combine (send / wait / invert / reduce).
+// Hand-written sm_100a kernels of the EP hot path: routing layout, dispatch and
+// combine, for a single rank and for a group of ranks on one NVLink domain.
 //
 // What they replace in the reference (paths inside the Mooncake tree):
 //   mooncake-ep/src/mooncake_ep_kernel.cu:138-470  `dispatch`
 //   mooncake-ep/src/mooncake_ep_kernel.cu:550-754  `combine`
 // Design differences, all deliberate:
-//   * no cooperative launch and no grid-wide barrier: a phase ends with its
-//     kernel, so no block of a kernel ever waits for another block of the same
-//     kernel; the only waits are on flags written by peers (bounded in time);
-//   * receive order is deterministic (source rank, then token index): slots
-//     come from a layout kernel instead of atomics in arrival order;
-//   * the token row is read once, quantised in registers and stored straight
-//     into every destination's receive staging (no local send staging pass);
-//   * work is split by (token, part-of-row) and by rows, not by expert, so the
-//     grid fills 148 SMs for 8 experts as well as for 256;
-//   * flags are 64-bit (call sequence number << 32 | value) and never cleaned.
+//   * receive order is deterministic (source rank, then token index): a token's
+//     row inside its expert is (first row of the source's segment) + (earlier
+//     tokens of the same source for that expert), never an atomic in arrival
+//     order;
+//   * dispatch has ONE data pass: the owner of an expert collects the counts
+//     every source announces, answers each source with the first row of its
+//     segment, and the source then stores the row - read once, quantised in
+//     registers - straight into its final place in the owner's packed receive
+//     area over NVLink (the reference stages the row locally, copies it to the
+//     owner's staging and copies it again into the packed output);
+//   * combine has ONE data pass over NVLink: expert outputs are made readable in
+//     symmetric memory, and the token owner reads its K rows from the experts'
+//     owners and reduces them in registers (the reference pushes every row into
+//     staging at the token owner first);
+//   * no cooperative launch, no grid-wide barrier; sender blocks depend on the
+//     control block (block 0, resident first) and on other GPUs only;
+//   * work is split by token and by row, not by expert, so the grid fills 148
+//     SMs for 8 experts as well as for 256;
+//   * the words ranks exchange are 64-bit (call sequence number << 32 | value)
+//     and are never cleaned.
 #include "ep_kernels.cuh"
 
 #include <atomic>
@@ -159,22 +169,61 @@ __device__ __forceinline__ int find_segment(const int* pre, int n, int g) {
     return lo;
 }
 
-// Decide one flag, once, for every block of the kernel.
+// =============================================================================
+// waiting for words of other ranks
+// =============================================================================
+// The timeout rule of mooncake-ep/src/mooncake_ep_kernel.cu:417-429 and :685-699:
+// after `timeout` the waiter clears active_ranks[src]; whoever sees the entry
+// cleared stops waiting. Every wait is also bounded by the hard limit.
+
 //
-// A flag is either seen to arrive (its word carries this call's sequence number)
-// or given up on (the rule of mooncake-ep/src/mooncake_ep_kernel.cu:417-429: after
-// `timeout` the waiter clears active_ranks[src]; whoever sees the entry cleared
-// stops waiting). Several blocks may need the same flag and they must agree, or
-// the receive layout would be torn; so the first block to reach a verdict
-// publishes it with a compare-and-swap into a local word, and every block -
-// including that one - takes the verdict from that word:
-//   resolved = seq << 32 | flag value     arrived
-//   resolved = seq << 32 | 0              given up
-// No block waits for another block: each keeps polling the peer's flag itself
-// until some verdict exists. Returns the flag's low word, or 0.
-__device__ __forceinline__ uint32_t resolve_flag(const WaitSpec& w, int i, int src,
-                                              bool primary = true) {
-    unsigned long long* res = reinterpret_cast<unsigned long long*>(w.resolved + i);
+// Waits of one dispatch call form a chain: an owner waits for the sources'
+// counts; a sender waits for the owner's answer, which a live owner may hold
+// back until it has given up on a dead source; a receiver waits for the senders'
+// payload words, which may be late for the same reason. So the answer is given
+// twice, and the payload word three times, the bound of the count - otherwise
+// one dead rank would make every live rank give up on every other. The dead
+// rank itself is still given up on after ONE timeout: whoever times out clears
+// its entry of the mask, and every waiter looks at the mask.
+__device__ __forceinline__ WaitCfg scaled(const WaitCfg& w, int times) {
+    WaitCfg r = w;
+    if (r.timeout_ns >= 0) r.timeout_ns *= times;
+    r.hard_timeout_ns *= times;
+    return r;
+}
+
+// One waiter per word (or waiters that may disagree harmlessly). Returns the
+// word's value (>= 1) or 0 when given up.
+__device__ __forceinline__ uint32_t wait_word(const uint64_t* word, uint32_t seq, const WaitCfg& w,
+                                              int src) {
+    uint64_t start = 0;
+    while (true) {
+        const uint64_t v = ld_acquire_sys(word);
+        if ((uint32_t)(v >> 32) == seq) return (uint32_t)v;
+        const uint64_t now = globaltimer_ns();
+        if (start == 0) start = now;
+        const int64_t waited = (int64_t)(now - start);
+        if (w.timeout_ns >= 0 && waited > w.timeout_ns) st_volatile_s32(w.active_ranks + src, 0);
+        if (waited > w.hard_timeout_ns) {
+            st_volatile_s32(w.active_ranks + src, 0);
+            atomicOr(w.status, kStatusHardTimeout);
+        }
+        if (!ld_volatile_s32(w.active_ranks + src)) return 0;
+    }
+}
+
+// Many waiters per word that must agree (or one token of a result would count a
+// rank in and the next would not): the first block to reach a verdict publishes
+// it with a compare-and-swap into a local word, and every block - that one
+// included - takes the verdict from that word:
+//   resolved = seq << 32 | value     arrived
+//   resolved = seq << 32 | 0         given up
+// No block waits for another block: each keeps polling the peer's word itself
+// until some verdict exists. Returns the value, or 0.
+__device__ __forceinline__ uint32_t resolve_flag(const uint64_t* flags, uint64_t* resolved, int i,
+                                                 uint32_t seq, const WaitCfg& w, int src,
+                                                 bool primary = true) {
+    unsigned long long* res = reinterpret_cast<unsigned long long*>(resolved + i);
     uint64_t start = 0;
     if (!primary) {
         // Many blocks want the same verdict. One of them (the "primary" for this
@@ -184,28 +233,28 @@ __device__ __forceinline__ uint32_t resolve_flag(const WaitSpec& w, int i, int s
         // work themselves - they never depend on the primary making progress.
         start = globaltimer_ns();
         while (globaltimer_ns() - start < 4000) {
-            const uint64_t r = ld_acquire_gpu(w.resolved + i);
-            if ((uint32_t)(r >> 32) == w.seq) {
+            const uint64_t r = ld_acquire_gpu(resolved + i);
+            if ((uint32_t)(r >> 32) == seq) {
                 const uint32_t v = (uint32_t)r;
-                if (v) (void)ld_acquire_sys(w.flags + i);
+                if (v) (void)ld_acquire_sys(flags + i);
                 return v;
             }
         }
     }
     while (true) {
         // both words are requested together: one round trip in the common case
-        const uint64_t r = ld_acquire_gpu(w.resolved + i);
-        const uint64_t f = ld_acquire_sys(w.flags + i);
-        if ((uint32_t)(r >> 32) == w.seq) {
+        const uint64_t r = ld_acquire_gpu(resolved + i);
+        const uint64_t f = ld_acquire_sys(flags + i);
+        if ((uint32_t)(r >> 32) == seq) {
             // decided already (possibly by another block). If it is an arrival,
             // the flag load above was our own acquire of the sender's release -
             // unless it raced ahead of the flag, then take it again.
             const uint32_t v = (uint32_t)r;
-            if (v && (uint32_t)(f >> 32) != w.seq) (void)ld_acquire_sys(w.flags + i);
+            if (v && (uint32_t)(f >> 32) != seq) (void)ld_acquire_sys(flags + i);
             return v;
         }
         unsigned long long mine;
-        if ((uint32_t)(f >> 32) == w.seq) {
+        if ((uint32_t)(f >> 32) == seq) {
             mine = (unsigned long long)f;  // arrived
         } else {
             const uint64_t now = globaltimer_ns();
@@ -217,41 +266,52 @@ __device__ __forceinline__ uint32_t resolve_flag(const WaitSpec& w, int i, int s
                 atomicOr(w.status, kStatusHardTimeout);
             }
             if (ld_volatile_s32(w.active_ranks + src)) continue;  // keep waiting
-            mine = (unsigned long long)w.seq << 32;               // given up
+            mine = (unsigned long long)seq << 32;                 // given up
         }
         // first verdict wins; the value the swap returns is the winner's
         const unsigned long long old = atomicCAS(res, (unsigned long long)r, mine);
         const unsigned long long verdict = (old == (unsigned long long)r) ? mine : old;
-        if ((uint32_t)(verdict >> 32) != w.seq) continue;  // lost to a stale word: look again
+        if ((uint32_t)(verdict >> 32) != seq) continue;  // lost to a stale word: look again
         const uint32_t v = (uint32_t)verdict;
-        if (v && (uint32_t)(f >> 32) != w.seq) (void)ld_acquire_sys(w.flags + i);
+        if (v && (uint32_t)(f >> 32) != seq) (void)ld_acquire_sys(flags + i);
         return v;
+    }
+}
+
+// A word another block of this GPU writes (the control block's verdicts). The
+// writer is resident before any reader and never waits for a reader.
+__device__ __forceinline__ uint32_t wait_local_word(const uint64_t* word, uint32_t seq,
+                                                    const WaitCfg& w) {
+    uint64_t start = 0;
+    while (true) {
+        const uint64_t v = ld_acquire_gpu(word);
+        if ((uint32_t)(v >> 32) == seq) return (uint32_t)v;
+        const uint64_t now = globaltimer_ns();
+        if (start == 0) start = now;
+        if ((int64_t)(now - start) > w.hard_timeout_ns) {
+            atomicOr(w.status, kStatusHardTimeout);
+            return 0;
+        }
     }
 }
 
 // =============================================================================
 // phase trace (diagnostic builds only: -DMCEP_PHASE_TRACE)
 // =============================================================================
-// Thread 0 of every block stamps the SM cycle counter at the phase boundaries
-// of the four bodies below (slot 0 also takes the global timer, so blocks can
-// be lined up against each other). Compiled out of the normal library.
+// Thread 0 of every block stamps the global nanosecond timer at phase
+// boundaries, so blocks - and kernels - can be lined up against each other.
+// Compiled out of the normal library.
 #ifdef MCEP_PHASE_TRACE
 constexpr int kTraceBodies = 4, kTraceBlocks = 1024, kTraceSlots = 8;
 __device__ unsigned long long g_phase_trace[kTraceBodies][kTraceBlocks][kTraceSlots];
-#define MCEP_TRACE(body, slot)                                                     \
-    do {                                                                           \
-        if (threadIdx.x == 0 && blockIdx.x < kTraceBlocks) {                       \
-            g_phase_trace[body][blockIdx.x][slot] = (unsigned long long)clock64(); \
-            if ((slot) == 0) g_phase_trace[body][blockIdx.x][kTraceSlots - 1] = globaltimer_ns(); \
-        }                                                                          \
+#define MCEP_TRACE(body, slot)                                              \
+    do {                                                                    \
+        if (threadIdx.x == 0 && blockIdx.x < kTraceBlocks)                  \
+            g_phase_trace[body][blockIdx.x][slot] = globaltimer_ns();       \
     } while (0)
-#define MCEP_TRACE_SYNC() __syncthreads()
 #else
 #define MCEP_TRACE(body, slot) \
     do {                       \
-    } while (0)
-#define MCEP_TRACE_SYNC() \
-    do {                  \
     } while (0)
 #endif
 
@@ -311,7 +371,6 @@ __global__ void __launch_bounds__(1024)
         if (lane == 0) {
             const int e = e0 + le;
             p.count[e] = carry;
-            if (p.done) p.done[e] = 0;
             if (p.recv_count) p.recv_count[e] = carry;
             if (p.layout_range) p.layout_range[e] = carry;  // begin 0 | count
         }
@@ -364,102 +423,142 @@ __global__ void __launch_bounds__(1024)
 }
 
 // =============================================================================
-// dispatch: send
+// sending token rows (single rank and groups)
 // =============================================================================
 // One block per token (blocks stride over the tokens), one warp per 512-channel
 // tile of the row. The block reads the bf16 row once (32 bytes per lane),
-// quantises it in registers when FP8 is on, and stores it to every selected
-// expert's slot: in the staged mode a message
-//   [32 B header: token index | payload | 16 B of scales per 512 channels]
-// in the owner rank's receive staging (peer memory over NVLink, or local), in
-// the direct mode (single rank) the packed outputs themselves.
+// quantises it in registers when FP8 is on, and stores it to the row of every
+// selected expert's packed receive area: this GPU's (single rank, or an expert
+// this rank owns) or a peer's, over NVLink.
 //
-// kFused: the slots are counted here instead of read from the layout kernel -
-// every block histograms the whole (small) index matrix in shared memory and
-// counts, for its own token, the earlier tokens that chose the same experts.
-// The host uses it when one block per token fits the machine in one wave.
+// kFused: the position of the token among this rank's tokens for each of its
+// experts is counted here instead of read from the layout kernel - every warp
+// takes whole tokens of the (small) index matrix. The host uses it when one
+// block per token fits the machine in one wave.
 //
-// Completion: messages are not fenced one by one. A block counts what it sent
-// per expert in shared memory; when its tokens are done it issues ONE
-// system-scope fence, then adds its counts to the per-expert totals. Whoever
-// completes an expert's total publishes the (source, expert) flag.
-__device__ __forceinline__ int topk_entry(const int64_t* topk_idx, int t, int K, int k, int E) {
-    // expert of entry (t, k); -1 when masked, out of range, or a repeat of an
-    // earlier entry of the same token
-    const int e = (int)__ldg(topk_idx + (size_t)t * K + k);
-    if (e < 0 || e >= E) return -1;
-    for (int kk = 0; kk < k; ++kk)
-        if ((int)__ldg(topk_idx + (size_t)t * K + kk) == e) return -1;
-    return e;
+// What goes where for entry (t, k) with expert e, owner rank o, local expert le,
+// row r = first row of this rank's segment in e + earlier tokens of this rank:
+//   payload    -> o's receive rows   [le][r][H e4m3 | H bf16]
+//   o == this rank: token index and scales go straight into the caller's
+//                   src_info / transposed scales tensors;
+//   o is a peer:    a side message [16 B: token index | 16 B of scales per 512
+//                   channels] goes to o's side area [le][r]; o's receive duty
+//                   moves it into its src_info / scales tensors.
+struct SendView {
+    const char* x;
+    const int64_t* topk_idx;
+    const int32_t* slot;
+    int T, K, E, R, M, H, rank;
+    int L, RM;
+    int32_t* status;
+    // rows this rank owns
+    char* recv_x;
+    float* recv_scales;
+    int32_t* recv_src_info;
+    int row_bytes;
+    // groups only
+    const uint64_t* beg;      // local words: first row of this rank's segment per expert
+    uint32_t seq;
+    WaitCfg wait;
+    size_t rx_off, meta_off;
+    int meta_stride;
+    int32_t* rowmap;
+    char* const* s_peer;      // shared-memory copies of the peer table and the mask
+    const int* s_active;
+};
+
+// One pass of all warps over the whole index matrix. With kHist it leaves the
+// whole-batch count per expert in hist[]; with t_own >= 0 it counts, for every
+// expert of token t_own (kmap: expert -> k), the earlier tokens that chose it
+// (s_before[k]). A repeated expert inside a token is counted once (lanes holding
+// the same (token, expert) elect the lowest lane).
+constexpr int kScanAhead = 4;
+
+template <bool kHist, bool kAhead>
+__device__ __forceinline__ void scan_index_matrix(const int64_t* topk_idx, int T, int K, int E,
+                                                  int* hist, const int* kmap, int* s_before,
+                                                  int t_own, const int (&e_ahead)[kScanAhead]) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int tpw = 32 / K;  // tokens per warp pass (K <= 16)
+    const int sk = lane % K, st = lane / K;
+    const bool lane_used = st < tpw;
+    auto count_pass = [&](int base, int e) {
+        const int t2 = base + st;
+        const bool valid = lane_used && t2 < T;
+        if (!valid || e >= E) e = -1;
+        const unsigned key = e >= 0 ? (((unsigned)st << 16) | (unsigned)e) : (0x80000000u | lane);
+        const unsigned grp = __match_any_sync(kFull, key);
+        if (e >= 0 && (int)(__ffs(grp) - 1) == lane) {
+            if (kHist) atomicAdd(&hist[e], 1);
+            if (t2 < t_own) {
+                const int kk = kmap[e];
+                if (kk >= 0) atomicAdd(&s_before[kk], 1);
+            }
+        }
+    };
+    if (kAhead) {
+#pragma unroll
+        for (int u = 0; u < kScanAhead; ++u) {
+            const int base = (warp + u * nwarps) * tpw;
+            if (base < T) count_pass(base, e_ahead[u]);
+        }
+    }
+    for (int base = (warp + (kAhead ? kScanAhead : 0) * nwarps) * tpw; base < T;
+         base += nwarps * tpw) {
+        const int t2 = base + st;
+        count_pass(base, (lane_used && t2 < T) ? (int)__ldg(topk_idx + (size_t)t2 * K + sk) : -1);
+    }
 }
 
-template <bool kFP8, bool kDirect, bool kFused>
-__device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, int* smem_i32) {
+
+// Requests the first kScanAhead passes of the scan (so the scan does not pay a
+// memory round trip per pass).
+__device__ __forceinline__ void scan_prefetch(const int64_t* topk_idx, int T, int K, bool on,
+                                              int (&e_ahead)[kScanAhead]) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int tpw = 32 / K;
+    const int sk = lane % K, st = lane / K;
+#pragma unroll
+    for (int u = 0; u < kScanAhead; ++u) {
+        const int t2 = (warp + u * nwarps) * tpw + st;
+        e_ahead[u] = -1;
+        if (on && st < tpw && t2 < T) e_ahead[u] = (int)__ldg(topk_idx + (size_t)t2 * K + sk);
+    }
+}
+
+template <bool kFP8, bool kGroup, bool kFused>
+__device__ __forceinline__ void send_tokens(const SendView& v, int first_token, int token_stride,
+                                            int* hist /* fused && !group: [E] */,
+                                            int* kmap /* fused: [E] */) {
     __shared__ char* s_dst[kMaxTopk];
+    __shared__ char* s_meta[kMaxTopk];
     __shared__ int s_exp[kMaxTopk];
-    __shared__ int s_slot[kMaxTopk];
+    __shared__ int s_le[kMaxTopk];
+    __shared__ int s_row[kMaxTopk];
     __shared__ int s_before[kMaxTopk];
     __shared__ int s_raw[kMaxTopk];
-    __shared__ int s_active[kMaxRanks];
-    __shared__ char* s_peer[kMaxRanks];
 
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
-    const int L = p.E / p.R;
-    const int RM = p.R * p.M;
-    const int nchunks = p.H / 16;
-    const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
-    const int S = p.H / 128;
-    const char* xb = reinterpret_cast<const char*>(p.x);
-    int* hist = smem_i32;                              // [E] whole-batch counts (fused)
-    int* kmap = smem_i32 + p.E;                        // [E] expert -> k of this block's token (fused)
-    int* cta_cnt = smem_i32 + (kFused ? 2 * p.E : 0);  // [E] sent by this block (staged)
+    const int nchunks = v.H / 16;
+    const int ntiles = (v.H + kTileChannels - 1) / kTileChannels;
+    const int S = v.H / 128;
 
-    pdl_wait();
-    pdl_launch_dependents();
-    MCEP_TRACE(0, 0);
-    // everything the block needs from memory is requested before the first
-    // barrier, so the routing work costs one memory round trip, not several
-    if (kFused)
-        for (int e = tid; e < p.E; e += nthr) hist[e] = 0, kmap[e] = -1;
-    if (!kDirect) {
-        for (int e = tid; e < p.E; e += nthr) cta_cnt[e] = 0;
-        for (int r = tid; r < p.R; r += nthr) {  // a block may have as few as 32 threads
-            s_active[r] = ld_volatile_s32(p.active_ranks + r);
-            s_peer[r] = reinterpret_cast<char*>(p.peer_base[r]);
-        }
-    }
-    // The tables above are read by other threads further down. The token loop
-    // has barriers of its own before any such read (and its first loads should
-    // not wait for this prologue), but a block without tokens skips the loop.
-    if ((int)blockIdx.x >= p.T) __syncthreads();
-
-    for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
-        const char* xrow = xb + (size_t)t * p.H * 2;
+    for (int t = first_token; t < v.T; t += token_stride) {
+        const char* xrow = v.x + (size_t)t * v.H * 2;
         V32 first = {};
         if (warp < ntiles && warp * 32 + lane < nchunks)
             first = ld32_readonly(xrow + (size_t)(warp * 32 + lane) * 32);
-        const bool scan_now = kFused && t == (int)blockIdx.x;
-        // the scan below lets a warp take whole tokens: lane -> (token, k)
-        const int tpw = 32 / p.K;            // tokens per warp pass (K <= 16)
-        const int sk = lane % p.K, st = lane / p.K;
-        const bool lane_used = st < tpw;
-        // the first kScanAhead passes of the scan are requested here, together
-        // with the row, so the scan does not pay a memory round trip per pass
-        constexpr int kScanAhead = 4;
+        // (in production a fused launch has one block per token; blocks that take
+        // several tokens - in-process groups - scan once per token)
+        const bool scan_now = kFused;
         int e_ahead[kScanAhead];
-#pragma unroll
-        for (int u = 0; u < kScanAhead; ++u) {
-            const int t2 = (warp + u * nwarps) * tpw + st;
-            e_ahead[u] = -1;
-            if (scan_now && lane_used && t2 < p.T)
-                e_ahead[u] = (int)__ldg(p.topk_idx + (size_t)t2 * p.K + sk);
-        }
+        scan_prefetch(v.topk_idx, v.T, v.K, scan_now, e_ahead);
         int my_slot = -1;
         if (tid < kMaxTopk) {
-            int e = tid < p.K ? (int)__ldg(p.topk_idx + (size_t)t * p.K + tid) : -1;
-            if (!kFused && tid < p.K) my_slot = __ldg(p.slot + (size_t)t * p.K + tid);
-            s_raw[tid] = (e >= 0 && e < p.E) ? e : -1;
+            int e = tid < v.K ? (int)__ldg(v.topk_idx + (size_t)t * v.K + tid) : -1;
+            if (!kFused && tid < v.K) my_slot = __ldg(v.slot + (size_t)t * v.K + tid);
+            s_raw[tid] = (e >= 0 && e < v.E) ? e : -1;
             s_before[tid] = 0;
         }
         __syncthreads();
@@ -472,61 +571,60 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
         }
         __syncthreads();
         if (scan_now) {
-            // One pass over the index matrix with every warp: whole-batch
-            // histogram, and for this block's token the number of earlier tokens
-            // per chosen expert. A repeated expert inside a token is counted once
-            // (lanes holding the same (token, expert) elect the lowest lane).
-            auto count_pass = [&](int base, int e) {
-                const int t2 = base + st;
-                const bool valid = lane_used && t2 < p.T;
-                if (!valid || e >= p.E) e = -1;
-                const unsigned key = e >= 0 ? (((unsigned)st << 16) | (unsigned)e) : (0x80000000u | lane);
-                const unsigned grp = __match_any_sync(kFull, key);
-                if (e >= 0 && (int)(__ffs(grp) - 1) == lane) {
-                    atomicAdd(&hist[e], 1);
-                    if (t2 < t) {
-                        const int kk = kmap[e];
-                        if (kk >= 0) atomicAdd(&s_before[kk], 1);
-                    }
-                }
-            };
-#pragma unroll
-            for (int u = 0; u < kScanAhead; ++u) {
-                const int base = (warp + u * nwarps) * tpw;
-                if (base < p.T) count_pass(base, e_ahead[u]);
-            }
-            for (int base = (warp + kScanAhead * nwarps) * tpw; base < p.T; base += nwarps * tpw) {
-                const int t2 = base + st;
-                count_pass(base, (lane_used && t2 < p.T) ? (int)__ldg(p.topk_idx + (size_t)t2 * p.K + sk)
-                                                         : -1);
-            }
+            if (kGroup)
+                scan_index_matrix<false, true>(v.topk_idx, v.T, v.K, v.E, nullptr, kmap, s_before,
+                                               t, e_ahead);
+            else
+                scan_index_matrix<true, true>(v.topk_idx, v.T, v.K, v.E, hist, kmap, s_before, t,
+                                              e_ahead);
             __syncthreads();
         }
         if (tid < kMaxTopk) {
             char* dst = nullptr;
-            int s = -1;
+            char* meta = nullptr;
+            int row = -1, le = 0;
             const int e = s_exp[tid];
             if (e >= 0) {
-                s = kFused ? s_before[tid] : my_slot;
-                if (s >= p.M) {
-                    atomicOr(p.status, kStatusSlotRange);
+                const int s = kFused ? s_before[tid] : my_slot;
+                if (s >= v.M) {
+                    atomicOr(v.status, kStatusSlotRange);
                 } else if (s >= 0) {
-                    if (kDirect) {
-                        dst = reinterpret_cast<char*>(p.recv_x) +
-                              ((size_t)e * RM + s) * (size_t)p.H * (kFP8 ? 1 : 2);
+                    if (!kGroup) {
+                        le = e;
+                        row = s;
+                        dst = v.recv_x + ((size_t)e * v.RM + s) * (size_t)v.row_bytes;
                     } else {
-                        const int dr = e / L;
-                        if (s_active[dr])
-                            dst = s_peer[dr] + p.stage_off +
-                                  ((size_t)((e - dr * L) * p.R + p.rank) * p.M + s) * p.msg_stride;
+                        const int dr = e / v.L;
+                        le = e - dr * v.L;
+                        if (v.s_active[dr]) {
+                            // the owner's answer: first row of this rank's segment
+                            const uint32_t b = wait_word(v.beg + e, v.seq, v.wait, dr);
+                            if (b) {
+                                row = (int)(b - 1) + s;
+                                if (row >= v.RM) {
+                                    atomicOr(v.status, kStatusSlotRange);
+                                    row = -1;
+                                } else if (dr == v.rank) {
+                                    dst = v.recv_x + ((size_t)le * v.RM + row) * (size_t)v.row_bytes;
+                                } else {
+                                    const size_t r = (size_t)le * v.RM + row;
+                                    dst = v.s_peer[dr] + v.rx_off + r * (size_t)v.row_bytes;
+                                    meta = v.s_peer[dr] + v.meta_off + r * (size_t)v.meta_stride;
+                                }
+                            }
+                        }
                     }
                 }
             }
+            if (kGroup && tid < v.K) v.rowmap[(size_t)t * v.K + tid] = row;
+            if (scan_now && e >= 0) kmap[e] = -1;  // leave the table clean for the next token
             s_dst[tid] = dst;
-            s_slot[tid] = s;
+            s_meta[tid] = meta;
+            s_le[tid] = le;
+            s_row[tid] = row;
         }
         __syncthreads();
-        if (t == (int)blockIdx.x) MCEP_TRACE(0, 1);  // routing of the first token is known
+        if (kGroup) MCEP_TRACE(0, 7);  // the owners' answers are in, rows can go
 
         for (int tile = warp; tile < ntiles; tile += nwarps) {
             const int c = tile * 32 + lane;
@@ -539,327 +637,84 @@ __device__ __forceinline__ void dispatch_send_body(const DispatchSendParams& p, 
             if (kFP8) {
                 float sinv;
                 const uint4 q = quantize16(cur, sinv);
-                if (kDirect) {
-#pragma unroll 4
-                    for (int k = 0; k < p.K; ++k) {
-                        char* d = s_dst[k];
-                        if (d == nullptr || !act) continue;
-                        st16(d + (size_t)c * 16, q);
-                        if ((lane & 7) == 0)
-                            p.recv_scales[((size_t)s_exp[k] * S + (c >> 3)) * RM + s_slot[k]] = sinv;
-                    }
-                } else {
-                    float4 sc;
+                float4 sc;
+                if (kGroup) {
                     sc.x = __shfl_sync(kFull, sinv, 0);
                     sc.y = __shfl_sync(kFull, sinv, 8);
                     sc.z = __shfl_sync(kFull, sinv, 16);
                     sc.w = __shfl_sync(kFull, sinv, 24);
+                }
 #pragma unroll 4
-                    for (int k = 0; k < p.K; ++k) {
-                        char* d = s_dst[k];
-                        if (d == nullptr) continue;
-                        if (act) st16(d + kHeaderBytes + (size_t)c * 16, q);
+                for (int k = 0; k < v.K; ++k) {
+                    char* d = s_dst[k];
+                    if (d == nullptr) continue;
+                    if (act) st16(d + (size_t)c * 16, q);
+                    char* m = kGroup ? s_meta[k] : nullptr;
+                    if (m != nullptr) {
                         if (lane == 0)
-                            st16(d + kHeaderBytes + p.H + (size_t)tile * 16,
+                            st16(m + kMetaHeaderBytes + (size_t)tile * 16,
                                  *reinterpret_cast<uint4*>(&sc));
+                    } else if (act && (lane & 7) == 0) {
+                        v.recv_scales[((size_t)s_le[k] * S + (c >> 3)) * v.RM + s_row[k]] = sinv;
                     }
                 }
             } else {
 #pragma unroll 4
-                for (int k = 0; k < p.K; ++k) {
+                for (int k = 0; k < v.K; ++k) {
                     char* d = s_dst[k];
                     if (d == nullptr || !act) continue;
-                    st32(d + (kDirect ? 0 : kHeaderBytes) + (size_t)c * 32, cur);
+                    st32(d + (size_t)c * 32, cur);
                 }
             }
         }
-        if (tid < p.K && s_dst[tid] != nullptr) {
-            if (kDirect) {
-                p.recv_src_info[(size_t)s_exp[tid] * RM + s_slot[tid]] = t;
-            } else {
-                st16(s_dst[tid], make_uint4((uint32_t)t, 0u, 0u, 0u));
-                atomicAdd(&cta_cnt[s_exp[tid]], 1);
-            }
+        if (tid < v.K && s_dst[tid] != nullptr) {
+            if (kGroup && s_meta[tid] != nullptr)
+                st16(s_meta[tid], make_uint4((uint32_t)t, 0u, 0u, 0u));
+            else
+                v.recv_src_info[(size_t)s_le[tid] * v.RM + s_row[tid]] = t;
         }
         __syncthreads();
     }
-
-    MCEP_TRACE(0, 2);  // all payload stores are issued
-    // per-expert duties, spread over the grid: the receive layout of a single
-    // rank, or the flag of an expert this rank sends nothing to
-    for (int e = blockIdx.x * nthr + tid; e < p.E; e += gridDim.x * nthr) {
-        const int c = kFused ? hist[e] : __ldg(p.count + e);
-        if (kDirect) {
-            if (kFused) {
-                p.recv_count[e] = c;
-                p.layout_range[e] = c;  // begin 0 | count
-            }
-        } else if (c == 0) {
-            const int dr = e / L;
-            if (s_active[dr]) {
-                uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[dr] + p.flag_off) +
-                              ((e - dr * L) * p.R + p.rank);
-                st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
-            }
-        }
-    }
-    if (!kDirect) {
-        // ONE system-scope fence for everything this block stored (it costs
-        // microseconds even when idle, so it is not paid per message), then the
-        // bookkeeping. Whoever completes an expert's total has, through the
-        // counter, observed every contributor's fence: all of that expert's
-        // messages are performed system-wide, and the flag may follow with only
-        // a device-scope fence in between.
-        MCEP_TRACE(0, 3);
-        if (tid == 0) __threadfence_system();
-        MCEP_TRACE(0, 4);  // the fence has returned
-        __syncthreads();
-        for (int e = tid; e < p.E; e += nthr) {
-            const int c = cta_cnt[e];
-            if (c == 0) continue;
-            const int total = kFused ? hist[e] : __ldg(p.count + e);
-            const int old = atomicAdd(p.done + e, c);
-            if (old + c == total) {
-                p.done[e] = 0;
-                __threadfence();
-                const int dr = e / L;
-                uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[dr] + p.flag_off) +
-                              ((e - dr * L) * p.R + p.rank);
-                st_relaxed_sys(f, ((uint64_t)p.seq << 32) | (uint32_t)(total + 1));
-            }
-        }
-    }
-    MCEP_TRACE(0, 5);
 }
 
 // =============================================================================
-// dispatch: receive - wait for the (source, expert) flags, fix the layout, pack
+// single rank: dispatch writes the packed outputs directly
 // =============================================================================
-// Every block first learns all L*R counts - one flag per thread, so the wait
-// costs one flag latency, and the verdict words make all blocks agree - and
-// turns them into the receive layout in shared memory: begin offsets per
-// (expert, source) and a global row prefix. Block 0 writes `layout_range` and
-// `recv_count`. Then rows are spread evenly over all warps of the grid (one
-// warp per row, loads batched ahead of stores), whatever the routing skew.
-constexpr int kRowWarps = 8;
-
-template <bool kFP8>
-__device__ __forceinline__ void dispatch_recv_body(const DispatchRecvParams& p, int* smem_i32) {
-    int* pre = smem_i32;                  // [L*R + 1] rows before each (expert, source)
-    int* beg = smem_i32 + p.L * p.R + 1;  // [L*R] first output row of each (expert, source)
-    __shared__ int s_wt[32];
+template <bool kFP8, bool kFused>
+__global__ void __launch_bounds__(512) ep_dispatch_send_direct_kernel(DirectDispatchParams p) {
+    extern __shared__ int smem_i32[];
+    int* hist = smem_i32;        // [E] whole-batch counts (fused)
+    int* kmap = smem_i32 + p.E;  // [E] expert -> k of this block's token (fused)
     const int tid = threadIdx.x, nthr = blockDim.x;
-    const int lane = tid & 31, warp = tid >> 5;
-    const int n = p.L * p.R;
-    const int RM = p.R * p.M;
-    const int nchunks = p.H / 16;
-    const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
-    const int S = p.H / 128;
     pdl_wait();
     pdl_launch_dependents();
-    MCEP_TRACE(1, 0);
-    for (int i = tid; i < n; i += nthr) {
-        const uint32_t v = resolve_flag(p.w, i, i % p.R, (i % gridDim.x) == blockIdx.x);
-        pre[i] = v ? (int)v - 1 : 0;
-    }
-    __syncthreads();
-    MCEP_TRACE(1, 1);  // every flag has a verdict
-    for (int le = tid; le < p.L; le += nthr) {
-        int run = 0;
-        for (int src = 0; src < p.R; ++src) {
-            const int c = pre[le * p.R + src];
-            beg[le * p.R + src] = run;
-            if (blockIdx.x == 0)
-                p.layout_range[le * p.R + src] = c ? (((int64_t)run << 32) | (int64_t)c) : 0;
-            run += c;
+    if (kFused)
+        for (int e = tid; e < p.E; e += nthr) hist[e] = 0, kmap[e] = -1;
+    // (the token loop has a barrier before the first use of these tables; a
+    // block without tokens only reads hist after the barrier below)
+    SendView v = {};
+    v.x = reinterpret_cast<const char*>(p.x), v.topk_idx = p.topk_idx, v.slot = p.slot;
+    v.T = p.T, v.K = p.K, v.E = p.E, v.R = 1, v.M = p.M, v.H = p.H, v.rank = 0;
+    v.L = p.E, v.RM = p.M, v.status = p.status;
+    v.recv_x = reinterpret_cast<char*>(p.recv_x), v.recv_scales = p.recv_scales;
+    v.recv_src_info = p.recv_src_info, v.row_bytes = p.H * (kFP8 ? 1 : 2);
+    send_tokens<kFP8, false, kFused>(v, blockIdx.x, gridDim.x, hist, kmap);
+    if (kFused) {
+        // the receive layout of a single rank, spread over the grid. A block
+        // without a token has not scanned: it has nothing to add (its share of
+        // the experts is written by... itself, so it scans now).
+        if ((int)blockIdx.x >= p.T) {
+            __syncthreads();
+            const int none[kScanAhead] = {-1, -1, -1, -1};
+            scan_index_matrix<true, false>(p.topk_idx, p.T, p.K, p.E, hist, kmap, nullptr, -1, none);
+            __syncthreads();
         }
-        if (blockIdx.x == 0) p.recv_count[le] = run;
-    }
-    __syncthreads();
-    block_exclusive_scan(pre, n, s_wt);
-    MCEP_TRACE(1, 2);  // layout done
-    const int total = pre[n];
-    const int nwarps = nthr >> 5;
-    // rows are dealt to the blocks one at a time (warp w of block b takes row
-    // w * grid + b, ...): a batch with fewer rows than the grid has warps still
-    // spreads over every SM
-    for (int g = warp * gridDim.x + blockIdx.x; g < total; g += gridDim.x * nwarps) {
-        const int i = find_segment(pre, n, g);
-        const int le = i / p.R;
-        const int j = g - pre[i];
-        const int row = beg[i] + j;
-        if (j >= p.M || row >= RM) {
-            if (lane == 0) atomicOr(p.w.status, kStatusSlotRange);
-            continue;
-        }
-        const char* msg = p.stage + ((size_t)i * p.M + j) * p.msg_stride;
-        const size_t out_row = (size_t)le * RM + row;
-        const int tok = lane == 0 ? ld_s32_coherent(msg) : 0;
-        if (kFP8) {
-            constexpr int kB = 8;  // 8 x 16 B per lane in flight
-            char* out = reinterpret_cast<char*>(p.recv_x) + out_row * p.H;
-            float sc0 = 0.f, sc1 = 0.f;
-            if (lane < S) sc0 = ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)lane * 4);
-            if (lane + 32 < S) sc1 = ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)(lane + 32) * 4);
-            for (int t0 = 0; t0 < ntiles; t0 += kB) {
-                uint4 v[kB];
-#pragma unroll
-                for (int b = 0; b < kB; ++b) {
-                    const int c = (t0 + b) * 32 + lane;
-                    if (t0 + b < ntiles && c < nchunks)
-                        v[b] = ld16_coherent(msg + kHeaderBytes + (size_t)c * 16);
-                }
-#pragma unroll
-                for (int b = 0; b < kB; ++b) {
-                    const int c = (t0 + b) * 32 + lane;
-                    if (t0 + b < ntiles && c < nchunks) st16(out + (size_t)c * 16, v[b]);
-                }
-            }
-            if (lane < S) p.recv_scales[((size_t)le * S + lane) * RM + row] = sc0;
-            if (lane + 32 < S) p.recv_scales[((size_t)le * S + lane + 32) * RM + row] = sc1;
-            for (int gi = lane + 64; gi < S; gi += 32)  // hidden > 8192
-                p.recv_scales[((size_t)le * S + gi) * RM + row] =
-                    ld_f32_coherent(msg + kHeaderBytes + p.H + (size_t)gi * 4);
-        } else {
-            constexpr int kB = 4;  // 4 x 32 B per lane in flight
-            char* out = reinterpret_cast<char*>(p.recv_x) + out_row * p.H * 2;
-            for (int t0 = 0; t0 < ntiles; t0 += kB) {
-                V32 v[kB];
-#pragma unroll
-                for (int b = 0; b < kB; ++b) {
-                    const int c = (t0 + b) * 32 + lane;
-                    if (t0 + b < ntiles && c < nchunks)
-                        v[b] = ld32_coherent(msg + kHeaderBytes + (size_t)c * 32);
-                }
-#pragma unroll
-                for (int b = 0; b < kB; ++b) {
-                    const int c = (t0 + b) * 32 + lane;
-                    if (t0 + b < ntiles && c < nchunks) st32(out + (size_t)c * 32, v[b]);
-                }
-            }
-        }
-        if (lane == 0) p.recv_src_info[out_row] = tok;
-    }
-    MCEP_TRACE_SYNC();
-    MCEP_TRACE(1, 3);
-}
-
-// =============================================================================
-// combine: send expert outputs back to the token owners
-// =============================================================================
-// One warp per packed row (warps stride over the rows), loads batched ahead of
-// the stores. Row r of local expert le that came from rank d's token t goes to
-// d's combine staging slot [global expert][t] (the slot rule of
-// mooncake-ep/src/mooncake_ep_kernel.cu:633-637). Completion is counted per
-// (expert, destination) segment the same way dispatch counts per expert: one
-// system fence per block, then the block's shared-memory counts are added to
-// the global ones and whoever completes a segment publishes that expert's flag
-// at d.
-__device__ __forceinline__ void combine_send_body(const CombineSendParams& p, int* smem_i32) {
-    int* pre = smem_i32;                      // [L*R + 1]
-    int* cta_cnt = smem_i32 + p.L * p.R + 1;  // [L*R]
-    __shared__ int s_wt[32];
-    __shared__ int s_active[kMaxRanks];
-    __shared__ char* s_peer[kMaxRanks];
-    const int tid = threadIdx.x, nthr = blockDim.x;
-    const int lane = tid & 31, warp = tid >> 5;
-    const int n = p.L * p.R;
-    const int RM = p.R * p.M;
-    const int nchunks = p.H / 16;
-    const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
-    pdl_wait();
-    pdl_launch_dependents();
-    MCEP_TRACE(2, 0);
-    for (int i = tid; i < n; i += nthr) {
-        pre[i] = (int)(__ldg(p.layout_range + i) & 0xffffffffll);
-        cta_cnt[i] = 0;
-    }
-    for (int r = tid; r < p.R; r += nthr) {
-        s_active[r] = ld_volatile_s32(p.active_ranks + r);
-        s_peer[r] = reinterpret_cast<char*>(p.peer_base[r]);
-    }
-    __syncthreads();
-    // empty segments: flag right away
-    for (int i = blockIdx.x * nthr + tid; i < n; i += gridDim.x * nthr) {
-        if (pre[i] == 0) {
-            const int d = i % p.R, le = i / p.R;
-            if (s_active[d]) {
-                uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[d] + p.flag_off) + (p.rank * p.L + le);
-                st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
-            }
+        for (int e = blockIdx.x * nthr + tid; e < p.E; e += gridDim.x * nthr) {
+            const int c = hist[e];
+            p.recv_count[e] = c;
+            p.layout_range[e] = c;  // begin 0 | count
         }
     }
-    __syncthreads();
-    block_exclusive_scan(pre, n, s_wt);
-    MCEP_TRACE(2, 1);  // layout read and scanned
-    const int total = pre[n];
-    const char* xb = reinterpret_cast<const char*>(p.x);
-    constexpr int kB = 8;  // 8 x 32 B per lane in flight: a 7168-wide row takes two round trips
-    const int nwarps = nthr >> 5;
-    // rows dealt to the blocks one at a time, as in the dispatch receive phase
-    for (int g = warp * gridDim.x + blockIdx.x; g < total; g += gridDim.x * nwarps) {
-        const int i = find_segment(pre, n, g);
-        const int le = i / p.R, d = i - le * p.R;
-        const int j = g - pre[i];
-        const int row = (int)(__ldg(p.layout_range + i) >> 32) + j;
-        const bool live = s_active[d] != 0;
-        const bool row_ok = row < RM;
-        // the source row does not depend on the token index: request it together
-        // with the index so the two loads overlap
-        int t = -1;
-        if (row_ok) t = __ldg(p.src_info + (size_t)le * RM + row);
-        const char* src = xb + ((size_t)le * RM + (row_ok ? row : 0)) * p.H * 2;
-        V32 v[kB];
-#pragma unroll
-        for (int b = 0; b < kB; ++b) {
-            const int c = b * 32 + lane;
-            if (live && row_ok && b < ntiles && c < nchunks) v[b] = ld32_readonly(src + (size_t)c * 32);
-        }
-        if (t < 0 || t >= p.M) {
-            if (lane == 0) atomicOr(p.status, kStatusBadSource);
-        } else if (live) {
-            char* dst = s_peer[d] + p.stage_off + ((size_t)(p.rank * p.L + le) * p.M + t) * p.H * 2;
-#pragma unroll
-            for (int b = 0; b < kB; ++b) {
-                const int c = b * 32 + lane;
-                if (b < ntiles && c < nchunks) st32(dst + (size_t)c * 32, v[b]);
-            }
-            for (int t0 = kB; t0 < ntiles; t0 += kB) {
-#pragma unroll
-                for (int b = 0; b < kB; ++b) {
-                    const int c = (t0 + b) * 32 + lane;
-                    if (t0 + b < ntiles && c < nchunks) v[b] = ld32_readonly(src + (size_t)c * 32);
-                }
-#pragma unroll
-                for (int b = 0; b < kB; ++b) {
-                    const int c = (t0 + b) * 32 + lane;
-                    if (t0 + b < ntiles && c < nchunks) st32(dst + (size_t)c * 32, v[b]);
-                }
-            }
-        }
-        if (lane == 0) atomicAdd(&cta_cnt[i], 1);
-    }
-    __syncthreads();
-    MCEP_TRACE(2, 2);  // all rows are issued
-    if (tid == 0) __threadfence_system();
-    MCEP_TRACE(2, 3);  // the fence has returned
-    __syncthreads();
-    for (int i = tid; i < n; i += nthr) {
-        const int c = cta_cnt[i];
-        if (c == 0) continue;
-        const int cnt = (int)(__ldg(p.layout_range + i) & 0xffffffffll);
-        const int old = atomicAdd(p.done + i, c);
-        if (old + c == cnt) {
-            p.done[i] = 0;
-            const int d = i % p.R, le = i / p.R;
-            if (s_active[d]) {
-                __threadfence();  // see the dispatch send kernel: one system fence per block
-                uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[d] + p.flag_off) + (p.rank * p.L + le);
-                st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
-            }
-        }
-    }
-    MCEP_TRACE(2, 4);
 }
 
 // Single rank: rowmap[t][k] = packed row of (token t, expert topk[t][k]) as the
@@ -892,37 +747,71 @@ __global__ void __launch_bounds__(256) ep_combine_invert_kernel(CombineInvertPar
 }
 
 // =============================================================================
-// combine: weighted top-k reduction
+// weighted top-k reduction
 // =============================================================================
 // One block per token, one warp per 512-channel tile; each lane owns 16
 // channels: up to K 32-byte loads in flight, fp32 FMA accumulation in k order,
 // one bf16 rounding, one 32-byte store (mooncake_ep_kernel.cu:715-752).
-// kDepth rows are requested before the first of them is used: 8 when there is
-// one block per SM anyway (small batches), 4 when several blocks share an SM.
-template <bool kDirect, int kDepth>
-__device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p) {
+// kDepth rows are requested before the first of them is used. s_ptr has kMaxTopk
+// entries, null where nothing is to be added.
+template <int kDepth, bool kReadOnly>
+__device__ __forceinline__ void reduce_rows(const char* const* s_ptr, const float* s_w, int K,
+                                            int H, void* out_row) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int nchunks = H / 16;
+    const int ntiles = (H + kTileChannels - 1) / kTileChannels;
+    for (int tile = warp; tile < ntiles; tile += nwarps) {
+        const int c = tile * 32 + lane;
+        if (c >= nchunks) continue;
+        float acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+        for (int k0 = 0; k0 < K; k0 += kDepth) {
+            V32 v[kDepth];
+#pragma unroll
+            for (int b = 0; b < kDepth; ++b) {
+                const char* rp = s_ptr[k0 + b];
+                if (rp != nullptr)
+                    v[b] = kReadOnly ? ld32_readonly(rp + (size_t)c * 32)
+                                     : ld32_coherent(rp + (size_t)c * 32);
+            }
+#pragma unroll
+            for (int b = 0; b < kDepth; ++b) {
+                if (s_ptr[k0 + b] == nullptr) continue;
+                const float wk = s_w[k0 + b];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    acc[2 * i] = fmaf(bf16lo(v[b].w[i]), wk, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(bf16hi(v[b].w[i]), wk, acc[2 * i + 1]);
+                }
+            }
+        }
+        st32(reinterpret_cast<char*>(out_row) + (size_t)c * 32, pack_bf16x16(acc));
+    }
+}
+
+template <int kDepth>
+__global__ void __launch_bounds__(512) ep_combine_reduce_direct_kernel(DirectCombineParams p) {
+    static_assert(kMaxTopk % kDepth == 0, "the row batches must tile the top-k table");
     __shared__ const char* s_ptr[kMaxTopk];
     __shared__ float s_w[kMaxTopk];
     __shared__ int s_row[kMaxTopk];
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
-    const int nchunks = p.H / 16;
-    const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
     pdl_wait();
     pdl_launch_dependents();
-    MCEP_TRACE(3, 0);
     for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
         int e = -1, r = 0;
         float w = 0.f;
         if (tid < p.K) {
             e = (int)__ldg(p.topk_idx + (size_t)t * p.K + tid);
             w = __ldg(p.topk_weights + (size_t)t * p.K + tid);
-            if (kDirect && !p.search) r = __ldcg(p.rowmap + (size_t)t * p.K + tid);
+            if (!p.search) r = __ldcg(p.rowmap + (size_t)t * p.K + tid);
         }
-        if (kDirect && p.search) {
+        if (p.search) {
             // Small batches: no separate inversion pass. Warp k looks the token
-            // up in the handle itself - the segment of expert topk[t][k] that
-            // came from this (only) rank - 32 entries of src_info at a time.
+            // up in the handle itself - the segment of expert topk[t][k] - 32
+            // entries of src_info at a time.
             for (int k = warp; k < p.K; k += nwarps) {
                 const int ek = (int)__ldg(p.topk_idx + (size_t)t * p.K + k);
                 int row = -1;
@@ -931,8 +820,8 @@ __device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p
                     const int cnt = (int)(lr & 0xffffffffll), begin = (int)(lr >> 32);
                     for (int j0 = 0; j0 < cnt; j0 += 32) {
                         const int j = begin + j0 + lane;
-                        const bool hit = j0 + lane < cnt && j < p.RM &&
-                                         __ldg(p.src_info + (size_t)ek * p.RM + j) == t;
+                        const bool hit = j0 + lane < cnt && j < p.M &&
+                                         __ldg(p.src_info + (size_t)ek * p.M + j) == t;
                         const unsigned m = __ballot_sync(kFull, hit);
                         if (m) {
                             row = begin + j0 + __ffs(m) - 1;
@@ -946,120 +835,546 @@ __device__ __forceinline__ void combine_reduce_body(const CombineReduceParams& p
         __syncthreads();  // s_row is in place; the previous token's rows are done with s_ptr
         if (tid < kMaxTopk) {
             const char* ptr = nullptr;
-            if (kDirect && p.search && tid < p.K) r = s_row[tid];
+            if (p.search && tid < p.K) r = s_row[tid];
             if (tid < p.K && e >= 0 && e < p.E) {
-                const int owner = e / p.L;
-                if (kDirect) {
-                    if (ld_volatile_s32(p.active_ranks + owner) && r >= 0 && r < p.RM)
-                        ptr = reinterpret_cast<const char*>(p.x) + ((size_t)e * p.RM + r) * p.H * 2;
-                } else {
-                    // wait for this expert's rows (mooncake_ep_kernel.cu:685-699), then the
-                    // mask decides (an owner that timed out is skipped, :728-732)
-                    const uint32_t v = resolve_flag(p.w, e, owner);
-                    if (v && ld_volatile_s32(p.active_ranks + owner))
-                        ptr = p.stage + ((size_t)e * p.M + t) * p.H * 2;
+                if (ld_volatile_s32(p.active_ranks) && r >= 0 && r < p.M)
+                    ptr = reinterpret_cast<const char*>(p.x) + ((size_t)e * p.M + r) * p.H * 2;
+            }
+            s_ptr[tid] = ptr;
+            s_w[tid] = w;
+        }
+        __syncthreads();
+        reduce_rows<kDepth, true>(s_ptr, s_w, p.K, p.H,
+                                  reinterpret_cast<char*>(p.combined_x) + (size_t)t * p.H * 2);
+    }
+}
+
+// =============================================================================
+// groups: dispatch
+// =============================================================================
+__device__ __forceinline__ void load_peer_tables(void* const* peer_base, const int32_t* active_ranks,
+                                                 int R, int32_t* status, char** s_peer,
+                                                 int* s_active) {
+    for (int r = threadIdx.x; r < R; r += blockDim.x) {
+        char* pb = reinterpret_cast<char*>(peer_base[r]);
+        int a = ld_volatile_s32(active_ranks + r);
+        if (a && pb == nullptr) {  // marked active but never mapped: leave it alone
+            atomicOr(status, kStatusNoPeer);
+            a = 0;
+        }
+        s_peer[r] = pb;
+        s_active[r] = a;
+    }
+}
+
+// The control block (block 0 of the send kernel).
+//  1. announce: count of this rank's tokens per expert -> the expert's owner;
+//  2. collect: for this rank's own experts, the counts of every active source
+//     (bounded wait; a source that does not answer is marked inactive and
+//     counts as zero);
+//  3. fix the receive layout (source-rank order), write `layout_range` and
+//     `recv_count`, leave the verdicts for the receive duty, and answer every
+//     source with the first row of its segment in each of this rank's experts.
+template <bool kFused>
+__device__ __forceinline__ void dispatch_control(const GroupDispatchParams& p, int* smem_i32,
+                                                 char* const* s_peer, const int* s_active) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int L = p.E / p.R, n = L * p.R;
+    int* hist = smem_i32;                       // [E] (fused)
+    int* s_cnt = smem_i32 + (kFused ? p.E : 0);  // [L*R]
+    int* s_beg = s_cnt + n;                      // [L*R]
+    MCEP_TRACE(0, 1);
+    if (kFused) {
+        int e_ahead[kScanAhead];
+        scan_prefetch(p.topk_idx, p.T, p.K, true, e_ahead);
+        for (int e = tid; e < p.E; e += nthr) hist[e] = 0;
+        __syncthreads();
+        scan_index_matrix<true, true>(p.topk_idx, p.T, p.K, p.E, hist, nullptr, nullptr, -1,
+                                      e_ahead);
+        __syncthreads();
+    }
+    for (int e = tid; e < p.E; e += nthr) {
+        const int dr = e / L;
+        if (!s_active[dr]) continue;
+        const int c = kFused ? hist[e] : __ldg(p.count + e);
+        uint64_t* wd = reinterpret_cast<uint64_t*>(s_peer[dr] + p.w.cnt_off) + (p.rank * L + (e - dr * L));
+        st_relaxed_sys(wd, ((uint64_t)p.seq << 32) | (uint32_t)(c + 1));
+    }
+    MCEP_TRACE(0, 2);  // counts announced
+    const uint64_t* my_cnt = reinterpret_cast<const uint64_t*>(p.local_base + p.w.cnt_off);
+    for (int i = tid; i < n; i += nthr) {
+        const int le = i / p.R, src = i - le * p.R;
+        int c = 0;
+        if (s_active[src]) {
+            const uint32_t v = wait_word(my_cnt + src * L + le, p.seq, p.wait, src);
+            c = v ? (int)v - 1 : 0;
+            if (c > p.M) {
+                atomicOr(p.wait.status, kStatusSlotRange);
+                c = 0;
+            }
+        }
+        s_cnt[i] = c;
+    }
+    __syncthreads();
+    MCEP_TRACE(0, 3);  // every source's counts are in
+    for (int le = tid; le < L; le += nthr) {
+        int run = 0;
+        for (int src = 0; src < p.R; ++src) {
+            const int c = s_cnt[le * p.R + src];
+            s_beg[le * p.R + src] = run;
+            p.layout_range[le * p.R + src] = c ? (((int64_t)run << 32) | (int64_t)c) : 0;
+            run += c;
+        }
+        p.recv_count[le] = run;
+    }
+    __syncthreads();
+    for (int i = tid; i < n; i += nthr) {
+        const int le = i / p.R, src = i - le * p.R;
+        // a source that went silent while its counts were awaited sent count 0
+        // and gets no answer
+        if (s_active[src] && ld_volatile_s32(p.wait.active_ranks + src)) {
+            uint64_t* wd = reinterpret_cast<uint64_t*>(s_peer[src] + p.w.beg_off) + (p.rank * L + le);
+            st_relaxed_sys(wd, ((uint64_t)p.seq << 32) | (uint32_t)(s_beg[i] + 1));
+        }
+        *reinterpret_cast<volatile uint64_t*>(p.res_cnt + i) =
+            ((uint64_t)p.seq << 32) | (uint32_t)(s_cnt[i] + 1);
+    }
+    MCEP_TRACE(0, 4);  // answers are out
+}
+
+// Receive duty of dispatch, shared by `np` participants (blocks): rows that
+// peers stored into this rank's receive area are complete once the source's
+// payload word has arrived; their side messages are then moved into the
+// caller's `src_info` and transposed `scales`, and - when the caller's recv_x
+// is not the in-place tensor - the rows themselves are copied out.
+// (Rows of experts this rank sent to itself need nothing: the sender wrote the
+// final tensors.)
+constexpr int kRowWarps = 8;
+
+template <bool kFP8>
+__device__ __forceinline__ void dispatch_recv_duty(const GroupDispatchParams& p, int j, int np,
+                                                   int* smem_i32) {
+    const int L = p.E / p.R, n = L * p.R;
+    int* pre = smem_i32;          // [n + 1] rows to process per (expert, source), then prefix
+    int* beg = smem_i32 + n + 1;  // [n] first row of each (expert, source)
+    __shared__ int s_wt[32];
+    __shared__ int s_ok[kMaxRanks];
+    __shared__ int s_tot[kMaxRanks];
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+    const int RM = p.R * p.M;
+    const int nchunks = p.H / 16;
+    const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
+    const int S = p.H / 128;
+    for (int r = tid; r < p.R; r += nthr) s_tot[r] = 0;
+    __syncthreads();
+    // the control block's verdicts: what every source sends to every local expert
+    for (int i = tid; i < n; i += nthr) {
+        const uint32_t v = wait_local_word(p.res_cnt + i, p.seq, scaled(p.wait, 2));
+        const int c = v ? (int)v - 1 : 0;
+        pre[i] = c;
+        if (c) atomicAdd(&s_tot[i % p.R], c);
+    }
+    __syncthreads();
+    for (int le = tid; le < L; le += nthr) {
+        int run = 0;
+        for (int src = 0; src < p.R; ++src) {
+            beg[le * p.R + src] = run;
+            run += pre[le * p.R + src];
+        }
+    }
+    __syncthreads();
+    // rows this rank sent to itself need nothing; all of the above, and the
+    // prefix below, is ready before the payload words are even looked at
+    for (int i = tid; i < n; i += nthr)
+        if (i % p.R == p.rank) pre[i] = 0;
+    __syncthreads();
+    block_exclusive_scan(pre, n, s_wt);
+    // a peer's rows count once its payload word is here (one verdict per source
+    // for all participants)
+    for (int r = tid; r < p.R; r += nthr) {
+        int ok = 0;
+        if (r != p.rank && s_tot[r] > 0) {
+            const uint64_t* flags = reinterpret_cast<const uint64_t*>(p.local_base + p.w.dflag_off);
+            ok = resolve_flag(flags, p.res_dflag, r, p.seq, scaled(p.wait, 3), r,
+                              np <= 80 || (j & 7) == (r & 7)) != 0;
+        }
+        s_ok[r] = ok;
+    }
+    __syncthreads();
+    MCEP_TRACE(1, 1);  // every payload word has a verdict
+    const int total = pre[n];
+    const char* rx = p.local_base + p.rx_off;
+    const char* mt = p.local_base + p.meta_off;
+    // rows are dealt to the participants one at a time (warp w of participant j
+    // takes row w * np + j, ...): a batch with fewer rows than there are warps
+    // still spreads over all of them
+    for (int g = warp * np + j; g < total; g += np * nwarps) {
+        const int i = find_segment(pre, n, g);
+        const int le = i / p.R;
+        if (!s_ok[i - le * p.R]) continue;  // a source that was given up on
+        const int row = beg[i] + (g - pre[i]);
+        if (row >= RM) {
+            if (lane == 0) atomicOr(p.wait.status, kStatusSlotRange);
+            continue;
+        }
+        const size_t r = (size_t)le * RM + row;
+        const char* meta = mt + r * (size_t)p.meta_stride;
+        // one round trip: the token index and 16 bytes (four scales) per lane are
+        // requested together, then scattered into the transposed scales
+        const int tok = lane == 31 ? ld_s32_coherent(meta) : 0;
+        if (kFP8) {
+            for (int q0 = 0; q0 < ntiles; q0 += 32) {
+                const int q = q0 + lane;
+                if (q >= ntiles) continue;
+                const uint4 sc = ld16_coherent(meta + kMetaHeaderBytes + (size_t)q * 16);
+                const uint32_t w4[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (4 * q + u < S)
+                        p.recv_scales[((size_t)le * S + 4 * q + u) * RM + row] = __uint_as_float(w4[u]);
+            }
+        }
+        if (lane == 31) p.recv_src_info[r] = tok;
+        if (!p.copy_rows) continue;
+        const char* src = rx + r * (size_t)p.row_bytes;
+        char* out = reinterpret_cast<char*>(p.recv_x) + r * (size_t)p.row_bytes;
+        if (kFP8) {
+            constexpr int kB = 8;  // 8 x 16 B per lane in flight
+            for (int t0 = 0; t0 < ntiles; t0 += kB) {
+                uint4 v[kB];
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks) v[b] = ld16_coherent(src + (size_t)c * 16);
+                }
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks) st16(out + (size_t)c * 16, v[b]);
+                }
+            }
+        } else {
+            constexpr int kB = 4;  // 4 x 32 B per lane in flight
+            for (int t0 = 0; t0 < ntiles; t0 += kB) {
+                V32 v[kB];
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks) v[b] = ld32_coherent(src + (size_t)c * 32);
+                }
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < ntiles && c < nchunks) st32(out + (size_t)c * 32, v[b]);
+                }
+            }
+        }
+    }
+    MCEP_TRACE(1, 2);
+}
+
+// Participants of the receive duty inside the one-launch kernel: the control
+// block and the last sender blocks to finish (at most this many).
+constexpr int kRecvHelpers = 64;
+
+// kPhases: 1 = control + send; 3 = control + send + receive duty (one launch).
+// `bid` of `nblocks`: the block's place in its rank's share of the grid (the
+// whole grid, except for in-process groups where one launch carries all ranks).
+template <bool kFP8, bool kFused, int kPhases>
+__device__ __forceinline__ void dispatch_body(const GroupDispatchParams& p, int bid, int nblocks,
+                                              int* smem_i32) {
+    __shared__ char* s_peer[kMaxRanks];
+    __shared__ int s_active[kMaxRanks];
+    __shared__ int s_ticket;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int nsend = nblocks - 1;
+    const int nh = nsend < kRecvHelpers ? nsend : kRecvHelpers;
+    MCEP_TRACE(0, 0);
+    load_peer_tables(p.peer_base, p.wait.active_ranks, p.R, p.wait.status, s_peer, s_active);
+
+    if (bid == 0) {
+        __syncthreads();
+        dispatch_control<kFused>(p, smem_i32, s_peer, s_active);
+        if (kPhases == 3) {
+            __syncthreads();
+            dispatch_recv_duty<kFP8>(p, nh, nh + 1, smem_i32);
+        }
+        return;
+    }
+
+    int* kmap = smem_i32;  // [E] (fused)
+    if (kFused)
+        for (int e = tid; e < p.E; e += nthr) kmap[e] = -1;
+    const int sid = bid - 1;
+    // (the token loop has barriers of its own before it reads the tables above;
+    // a block without tokens reads them only after the barrier below)
+    SendView v = {};
+    v.x = reinterpret_cast<const char*>(p.x), v.topk_idx = p.topk_idx, v.slot = p.slot;
+    v.T = p.T, v.K = p.K, v.E = p.E, v.R = p.R, v.M = p.M, v.H = p.H, v.rank = p.rank;
+    v.L = p.E / p.R, v.RM = p.R * p.M, v.status = p.wait.status;
+    v.recv_x = reinterpret_cast<char*>(p.recv_x), v.recv_scales = p.recv_scales;
+    v.recv_src_info = p.recv_src_info, v.row_bytes = p.row_bytes;
+    v.beg = reinterpret_cast<const uint64_t*>(p.local_base + p.w.beg_off);
+    v.seq = p.seq, v.wait = scaled(p.wait, 2), v.rx_off = p.rx_off, v.meta_off = p.meta_off;
+    v.meta_stride = p.meta_stride, v.rowmap = p.rowmap, v.s_peer = s_peer, v.s_active = s_active;
+    send_tokens<kFP8, true, kFused>(v, sid, nsend, nullptr, kmap);
+    MCEP_TRACE(0, 5);  // all rows of this block are issued
+
+    // Completion. Rows are not fenced one by one: the block issues ONE
+    // system-scope fence for everything it stored (it costs microseconds even
+    // when idle), then takes a ticket. Whoever takes the last ticket has,
+    // through the counter, observed every block's fence - all of this rank's
+    // rows are performed system-wide - and tells every peer with one word.
+    __syncthreads();
+    if (tid == 0) {
+        if (sid < p.T) __threadfence_system();
+        s_ticket = (int)atomicAdd(p.ticket, 1u);
+    }
+    __syncthreads();
+    MCEP_TRACE(0, 6);  // the fence has returned
+    const int ticket = s_ticket;
+    if (ticket == nsend - 1) {
+        if (tid == 0) *p.ticket = 0;
+        __threadfence();
+        for (int r = tid; r < p.R; r += nthr) {
+            if (r == p.rank || !s_active[r] || !ld_volatile_s32(p.wait.active_ranks + r)) continue;
+            uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[r] + p.w.dflag_off) + p.rank;
+            st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
+        }
+    }
+    if (kPhases == 3 && ticket >= nsend - nh) {
+        __syncthreads();
+        dispatch_recv_duty<kFP8>(p, ticket - (nsend - nh), nh + 1, smem_i32);
+    }
+}
+
+template <bool kFP8, bool kFused, int kPhases>
+__global__ void __launch_bounds__(512) ep_dispatch_kernel(GroupDispatchParams p) {
+    extern __shared__ int smem_i32[];
+    pdl_wait();
+    pdl_launch_dependents();
+    dispatch_body<kFP8, kFused, kPhases>(p, blockIdx.x, gridDim.x, smem_i32);
+}
+
+// In-process groups (several logical ranks on one GPU): the ranks' kernels wait
+// for one another, so they cannot be separate launches - nothing would
+// guarantee that they run at the same time. ONE cooperative launch carries all
+// ranks: consecutive runs of `per_rank` blocks do the work of one rank each.
+template <bool kFP8, bool kFused, int kPhases>
+__global__ void __launch_bounds__(512)
+    ep_dispatch_multi_kernel(const GroupDispatchParams* ps, int per_rank) {
+    extern __shared__ int smem_i32[];
+    __shared__ GroupDispatchParams s_p;
+    const int which = blockIdx.x / per_rank;
+    if (threadIdx.x == 0) s_p = ps[which];
+    __syncthreads();
+    dispatch_body<kFP8, kFused, kPhases>(s_p, blockIdx.x - which * per_rank, per_rank, smem_i32);
+}
+
+template <bool kFP8>
+__global__ void __launch_bounds__(kRowWarps * 32, 4) ep_dispatch_recv_kernel(GroupDispatchParams p) {
+    extern __shared__ int smem_i32[];
+    pdl_wait();
+    pdl_launch_dependents();
+    MCEP_TRACE(1, 0);
+    dispatch_recv_duty<kFP8>(p, blockIdx.x, gridDim.x, smem_i32);
+}
+
+// =============================================================================
+// groups: combine
+// =============================================================================
+// Publish duty, shared by `np` participants: rows of expert outputs that peers
+// will ask for (every segment of the handle whose source is another rank) are
+// copied into this rank's combine input in symmetric memory, same [expert][row]
+// position; one system fence per block, a ticket, and whoever finishes last
+// tells every peer. With zero copy the caller's kernels wrote the rows there
+// already and only the word is sent.
+__device__ __forceinline__ void combine_publish_duty(const GroupCombineParams& p, int j, int np,
+                                                     int* smem_i32, char* const* s_peer,
+                                                     const int* s_active) {
+    const int L = p.E / p.R, n = L * p.R;
+    int* pre = smem_i32;  // [n + 1]
+    __shared__ int s_wt[32];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+    const int RM = p.R * p.M;
+    const int nchunks = p.H / 16;
+    const int ntiles = (p.H + kTileChannels - 1) / kTileChannels;
+    bool stored = false;
+    if (!p.zero_copy) {
+        int* beg = smem_i32 + n + 1;  // [n] first row of each (expert, source) segment
+        for (int i = tid; i < n; i += nthr) {
+            const int src = i % p.R;
+            const long long lr = __ldg(p.layout_range + i);
+            int c = (int)(lr & 0xffffffffll);
+            if (src == p.rank || !s_active[src]) c = 0;
+            pre[i] = c;
+            beg[i] = (int)(lr >> 32);
+        }
+        __syncthreads();
+        block_exclusive_scan(pre, n, s_wt);
+        const int total = pre[n];
+        const char* xb = reinterpret_cast<const char*>(p.x);
+        char* cin = p.local_base + p.cin_off;
+        // A work item is a run of tiles of one row, sized so that the rows spread
+        // over every warp of the participants and an item's loads are all in
+        // flight at once (8 x 32 B per lane): the copy costs one memory round trip.
+        constexpr int kB = 8;
+        const int warps_total = np * nwarps;
+        int parts = total > 0 ? warps_total / total : 1;
+        if (parts < 1) parts = 1;
+        if (parts > ntiles) parts = ntiles;
+        int tpp = (ntiles + parts - 1) / parts;  // tiles per item
+        if (tpp > kB && parts < ntiles) tpp = kB;
+        parts = (ntiles + tpp - 1) / tpp;
+        const long long items = (long long)total * parts;
+        for (long long g = (long long)warp * np + j; g < items; g += (long long)np * nwarps) {
+            const int rg = (int)(g / parts), part = (int)(g - (long long)rg * parts);
+            const int i = find_segment(pre, n, rg);
+            const int le = i / p.R;
+            const int row = beg[i] + (rg - pre[i]);
+            if (row >= RM) {
+                if (lane == 0) atomicOr(p.wait.status, kStatusSlotRange);
+                continue;
+            }
+            const size_t off = ((size_t)le * RM + row) * (size_t)p.H * 2;
+            const int t_end = min(ntiles, (part + 1) * tpp);
+            for (int t0 = part * tpp; t0 < t_end; t0 += kB) {
+                V32 v[kB];
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < t_end && c < nchunks) v[b] = ld32_readonly(xb + off + (size_t)c * 32);
+                }
+#pragma unroll
+                for (int b = 0; b < kB; ++b) {
+                    const int c = (t0 + b) * 32 + lane;
+                    if (t0 + b < t_end && c < nchunks) st32(cin + off + (size_t)c * 32, v[b]);
+                }
+            }
+            stored = true;
+        }
+    }
+    // One fence for the block's rows, then the ticket (see the dispatch kernel).
+    // The rows were stored to THIS GPU's memory and peers read them through this
+    // GPU's L2, so a device-scope fence (about 1 us) is enough to order them
+    // before the word that goes out to the peers; the system-scope one (4 us and
+    // more) is for stores that cross NVLink.
+    const int any = __syncthreads_or(stored ? 1 : 0);
+    MCEP_TRACE(2, 3);  // this block's rows are copied
+    if (tid == 0) {
+        if (any || (p.zero_copy && j == 0)) __threadfence();
+        s_last = (atomicAdd(p.ticket, 1u) == (unsigned)(np - 1));
+        if (s_last) *p.ticket = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        __threadfence();
+        for (int r = tid; r < p.R; r += nthr) {
+            if (r == p.rank || !s_active[r]) continue;
+            uint64_t* f = reinterpret_cast<uint64_t*>(s_peer[r] + p.w.cflag_off) + p.rank;
+            st_relaxed_sys(f, ((uint64_t)p.seq << 32) | 1u);
+        }
+    }
+}
+
+// Reduce duty: one block per token. Row k of token t lives at the owner of
+// expert topk[t][k], at the row the dispatch call recorded; it is read from
+// there (a peer's combine input over NVLink once that peer's word has arrived,
+// or this rank's own expert output) and the K rows are reduced in registers.
+// An owner that is inactive, or whose word does not arrive in time (it is then
+// marked inactive), contributes nothing (mooncake_ep_kernel.cu:685-699, 728-732).
+__device__ __forceinline__ void combine_reduce_duty(const GroupCombineParams& p, int first_token,
+                                                    int token_stride, char* const* s_peer) {
+    __shared__ const char* s_ptr[kMaxTopk];
+    __shared__ float s_w[kMaxTopk];
+    const int tid = threadIdx.x;
+    const int L = p.E / p.R, RM = p.R * p.M;
+    const uint64_t* flags = reinterpret_cast<const uint64_t*>(p.local_base + p.w.cflag_off);
+    const char* own = p.zero_copy ? p.local_base + p.cin_off : reinterpret_cast<const char*>(p.x);
+    for (int t = first_token; t < p.T; t += token_stride) {
+        if (tid < kMaxTopk) {
+            const char* ptr = nullptr;
+            float w = 0.f;
+            if (tid < p.K) {
+                const int e = (int)__ldg(p.topk_idx + (size_t)t * p.K + tid);
+                w = __ldg(p.topk_weights + (size_t)t * p.K + tid);
+                const int row = __ldcg(p.rowmap + (size_t)t * p.K + tid);
+                if (e >= 0 && e < p.E && row >= 0 && row < RM) {
+                    const int o = e / L, le = e - o * L;
+                    const size_t off = ((size_t)le * RM + row) * (size_t)p.H * 2;
+                    if (o == p.rank) {
+                        if (ld_volatile_s32(p.wait.active_ranks + o)) ptr = own + off;
+                    } else if (ld_volatile_s32(p.wait.active_ranks + o) && s_peer[o] != nullptr) {
+                        const uint32_t v = resolve_flag(flags, p.res_cflag, o, p.seq, p.wait, o,
+                                                        ((first_token + o) & 7) == 0);
+                        if (v && ld_volatile_s32(p.wait.active_ranks + o))
+                            ptr = s_peer[o] + p.cin_off + off;
+                    }
                 }
             }
             s_ptr[tid] = ptr;
             s_w[tid] = w;
         }
         __syncthreads();
-        if (t == (int)blockIdx.x) MCEP_TRACE(3, 1);  // the first token's rows are located / have arrived
-        for (int tile = warp; tile < ntiles; tile += nwarps) {
-            const int c = tile * 32 + lane;
-            if (c >= nchunks) continue;
-            float acc[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = 0.f;
-            // s_ptr has kMaxTopk entries, null from K on
-            for (int k0 = 0; k0 < p.K; k0 += kDepth) {
-                V32 v[kDepth];
-#pragma unroll
-                for (int b = 0; b < kDepth; ++b) {
-                    const char* rp = s_ptr[k0 + b];
-                    if (rp != nullptr)
-                        v[b] = kDirect ? ld32_readonly(rp + (size_t)c * 32)
-                                       : ld32_coherent(rp + (size_t)c * 32);
-                }
-#pragma unroll
-                for (int b = 0; b < kDepth; ++b) {
-                    if (s_ptr[k0 + b] == nullptr) continue;
-                    const float wk = s_w[k0 + b];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        acc[2 * i] = fmaf(bf16lo(v[b].w[i]), wk, acc[2 * i]);
-                        acc[2 * i + 1] = fmaf(bf16hi(v[b].w[i]), wk, acc[2 * i + 1]);
-                    }
-                }
-            }
-            st32(reinterpret_cast<char*>(p.combined_x) + ((size_t)t * p.H + (size_t)c * 16) * 2,
-                 pack_bf16x16(acc));
-        }
+        if (t == first_token) MCEP_TRACE(2, 4);  // the owners' words are in, rows can be read
+        reduce_rows<8, false>(s_ptr, s_w, p.K, p.H,
+                              reinterpret_cast<char*>(p.combined_x) + (size_t)t * p.H * 2);
+        __syncthreads();  // the rows are done with s_ptr
     }
-    MCEP_TRACE_SYNC();
-    MCEP_TRACE(3, 2);
 }
 
-// =============================================================================
-// kernels
-// =============================================================================
-// The phases above as kernels of their own (hook mode, large batches), and the
-// two phases of a call as ONE kernel for small batches in a group: every block
-// first does its share of the send phase, then turns to the receive phase. The
-// receive phase waits for flags that this rank's own blocks publish at the end
-// of their send phase, so the grid is never larger than what is resident at
-// once (the launchers see to that); a block that has started never depends on a
-// block that has not.
-template <bool kFP8, bool kDirect, bool kFused>
-__global__ void __launch_bounds__(512) ep_dispatch_send_kernel(DispatchSendParams p) {
-    extern __shared__ int smem_i32[];
-    dispatch_send_body<kFP8, kDirect, kFused>(p, smem_i32);
-}
-
-template <bool kFP8>
-__global__ void __launch_bounds__(kRowWarps * 32, 4) ep_dispatch_recv_kernel(DispatchRecvParams p) {
-    extern __shared__ int smem_i32[];
-    dispatch_recv_body<kFP8>(p, smem_i32);
-}
-
-template <bool kFP8>
-__global__ void __launch_bounds__(512) ep_dispatch_kernel(DispatchSendParams sp, DispatchRecvParams rp) {
-    extern __shared__ int smem_i32[];
-    dispatch_send_body<kFP8, false, true>(sp, smem_i32);
+// kPhases: 1 = publish, 2 = reduce, 3 = both in one launch.
+template <int kPhases>
+__device__ __forceinline__ void combine_body(const GroupCombineParams& p, int bid, int nblocks,
+                                             int* smem_i32) {
+    __shared__ char* s_peer[kMaxRanks];
+    __shared__ int s_active[kMaxRanks];
+    MCEP_TRACE(2, 0);
+    load_peer_tables(p.peer_base, p.wait.active_ranks, p.R, p.wait.status, s_peer, s_active);
     __syncthreads();
-    dispatch_recv_body<kFP8>(rp, smem_i32);
+    if (kPhases & 1) combine_publish_duty(p, bid, nblocks, smem_i32, s_peer, s_active);
+    MCEP_TRACE(2, 1);
+    if (kPhases & 2) {
+        __syncthreads();
+        combine_reduce_duty(p, bid, nblocks, s_peer);
+    }
+    MCEP_TRACE(2, 2);
 }
 
-__global__ void __launch_bounds__(kRowWarps * 32) ep_combine_send_kernel(CombineSendParams p) {
+template <int kPhases>
+__global__ void __launch_bounds__(512) ep_combine_kernel(GroupCombineParams p) {
     extern __shared__ int smem_i32[];
-    combine_send_body(p, smem_i32);
+    pdl_wait();
+    pdl_launch_dependents();
+    combine_body<kPhases>(p, blockIdx.x, gridDim.x, smem_i32);
 }
 
-template <bool kDirect, int kDepth>
-__global__ void __launch_bounds__(512) ep_combine_reduce_kernel(CombineReduceParams p) {
-    static_assert(kMaxTopk % kDepth == 0, "the row batches must tile the top-k table");
-    combine_reduce_body<kDirect, kDepth>(p);
-}
-
-__global__ void __launch_bounds__(512) ep_combine_kernel(CombineSendParams sp, CombineReduceParams rp) {
+// All logical ranks of an in-process group in one cooperative launch (see
+// ep_dispatch_multi_kernel).
+__global__ void __launch_bounds__(512)
+    ep_combine_multi_kernel(const GroupCombineParams* ps, int per_rank) {
     extern __shared__ int smem_i32[];
-    combine_send_body(sp, smem_i32);
+    __shared__ GroupCombineParams s_p;
+    const int which = blockIdx.x / per_rank;
+    if (threadIdx.x == 0) s_p = ps[which];
     __syncthreads();
-    combine_reduce_body<false, 8>(rp);
+    combine_body<3>(s_p, blockIdx.x - which * per_rank, per_rank, smem_i32);
 }
 
 // threads per block: one warp per tile, at most 16 warps
-inline int block_threads(int H) {
+inline int block_threads(int H, int at_least = 32) {
     int ntiles = (H + kTileChannels - 1) / kTileChannels;
     if (ntiles > 16) ntiles = 16;
     if (ntiles < 1) ntiles = 1;
-    return ntiles * 32;
+    int t = ntiles * 32;
+    return t < at_least ? at_least : t;
 }
-// a grid that fills the machine once (blocks stride over the work items):
-// as many blocks as are resident at a time for this kernel, block size and
-// shared memory
+// how many blocks of this kernel are resident at a time on the whole device
 template <typename K>
-inline int persistent_grid(long long items, K kernel, int threads, size_t smem, const LaunchCtx& ctx) {
+inline long long resident_blocks(K kernel, int threads, size_t smem, const LaunchCtx& ctx) {
     // the occupancy query is not free: remember the answer per (kernel, block, smem)
     static std::mutex mu;
     static std::map<std::tuple<const void*, int, size_t>, int> cache;
@@ -1080,7 +1395,12 @@ inline int persistent_grid(long long items, K kernel, int threads, size_t smem, 
             cache[key] = per_sm;
         }
     }
-    long long cap = (long long)ctx.num_sms * per_sm;
+    return (long long)ctx.num_sms * per_sm;
+}
+// a grid that fills the machine once (blocks stride over the work items)
+template <typename K>
+inline int persistent_grid(long long items, K kernel, int threads, size_t smem, const LaunchCtx& ctx) {
+    const long long cap = resident_blocks(kernel, threads, smem, ctx);
     long long g = items < cap ? items : cap;
     return (int)(g < 1 ? 1 : g);
 }
@@ -1118,85 +1438,25 @@ cudaError_t launch_layout(const LayoutParams& p, const LaunchCtx& ctx) {
                   ctx, p, epc, words);
 }
 
-bool dispatch_send_can_fuse_layout(int T, int K, int H, int num_sms) {
-    // one block per token in a single wave, and an index matrix small enough to
-    // be scanned by every block
-    (void)H;
-    // one block per token, all resident at once even at two blocks per SM
-    return (long long)T * K <= 4096 && T <= num_sms * 2;
+bool can_fuse_layout(int T, int K, int E, int num_sms) {
+    // one block per token, all resident at once even at two blocks per SM, an
+    // index matrix small enough to be scanned by every block, and expert tables
+    // that fit the static shared-memory budget
+    return (long long)T * K <= 4096 && T <= num_sms * 2 && E <= 2048;
 }
 
-cudaError_t launch_dispatch_send(const DispatchSendParams& p, const LaunchCtx& ctx) {
+cudaError_t launch_direct_dispatch(const DirectDispatchParams& p, const LaunchCtx& ctx) {
     const int threads = block_threads(p.H);
-    const size_t smem = (size_t)((p.fused ? 2 * p.E : 0) + (p.direct ? 0 : p.E)) * sizeof(int);
-    void (*k)(DispatchSendParams) = nullptr;
-    const int sel = (p.use_fp8 ? 4 : 0) | (p.direct ? 2 : 0) | (p.fused ? 1 : 0);
-    switch (sel) {
-        case 0: k = ep_dispatch_send_kernel<false, false, false>; break;
-        case 1: k = ep_dispatch_send_kernel<false, false, true>; break;
-        case 2: k = ep_dispatch_send_kernel<false, true, false>; break;
-        case 3: k = ep_dispatch_send_kernel<false, true, true>; break;
-        case 4: k = ep_dispatch_send_kernel<true, false, false>; break;
-        case 5: k = ep_dispatch_send_kernel<true, false, true>; break;
-        case 6: k = ep_dispatch_send_kernel<true, true, false>; break;
-        default: k = ep_dispatch_send_kernel<true, true, true>; break;
+    const size_t smem = (size_t)(p.fused ? 2 * p.E : 0) * sizeof(int);
+    void (*k)(DirectDispatchParams) = nullptr;
+    switch ((p.use_fp8 ? 2 : 0) | (p.fused ? 1 : 0)) {
+        case 0: k = ep_dispatch_send_direct_kernel<false, false>; break;
+        case 1: k = ep_dispatch_send_direct_kernel<false, true>; break;
+        case 2: k = ep_dispatch_send_direct_kernel<true, false>; break;
+        default: k = ep_dispatch_send_direct_kernel<true, true>; break;
     }
     const int grid = p.fused ? (p.T > 0 ? p.T : 1) : persistent_grid(p.T, k, threads, smem, ctx);
-    return launch(p.direct ? "ep_dispatch_send_direct" : "ep_dispatch_send", k, dim3(grid),
-                  dim3(threads), smem, ctx, p);
-}
-
-cudaError_t launch_dispatch_recv(const DispatchRecvParams& p, const LaunchCtx& ctx) {
-    const int threads = kRowWarps * 32;
-    const size_t smem = (size_t)(2 * p.L * p.R + 1) * sizeof(int);
-    auto k = p.use_fp8 ? ep_dispatch_recv_kernel<true> : ep_dispatch_recv_kernel<false>;
-    // The row count is only known on the device. Under even routing a rank
-    // receives about what it sends (`expected_rows`); the grid is sized for
-    // twice that - blocks stride, so a skewed or larger load is still covered -
-    // and never beyond one resident wave.
-    long long rows = 2ll * p.expected_rows;
-    const long long worst = (long long)p.L * p.R * p.M;
-    if (rows > worst) rows = worst;
-    const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, k, threads, smem, ctx);
-    return launch("ep_dispatch_recv", k, dim3(grid), dim3(threads), smem, ctx, p);
-}
-
-cudaError_t launch_combine_send(const CombineSendParams& p, const LaunchCtx& ctx) {
-    const int threads = kRowWarps * 32;
-    const long long rows = (long long)p.L * p.R * p.M;
-    const size_t smem = (size_t)(2 * p.L * p.R + 1) * sizeof(int);
-    const int grid = persistent_grid((rows + kRowWarps - 1) / kRowWarps, ep_combine_send_kernel,
-                                     threads, smem, ctx);
-    return launch("ep_combine_send", ep_combine_send_kernel, dim3(grid), dim3(threads), smem, ctx, p);
-}
-
-bool call_can_be_one_kernel(int T, int K, int H, int num_sms) {
-    // small batch, one block per token resident at two blocks per SM (dispatch) and
-    // at one block per SM for the register-heavier combine
-    (void)H;
-    return (long long)T * K <= 4096 && T <= num_sms;
-}
-
-cudaError_t launch_dispatch_one_kernel(const DispatchSendParams& sp, const DispatchRecvParams& rp,
-                                       const LaunchCtx& ctx) {
-    const int threads = block_threads(sp.H);
-    size_t smem = (size_t)3 * sp.E * sizeof(int);
-    const size_t smem_recv = (size_t)(2 * rp.L * rp.R + 1) * sizeof(int);
-    if (smem_recv > smem) smem = smem_recv;
-    auto k = sp.use_fp8 ? ep_dispatch_kernel<true> : ep_dispatch_kernel<false>;
-    const int grid = sp.T > 0 ? sp.T : 1;
-    if (grid > persistent_grid(grid, k, threads, smem, ctx)) return cudaErrorInvalidConfiguration;
-    return launch("ep_dispatch", k, dim3(grid), dim3(threads), smem, ctx, sp, rp);
-}
-
-cudaError_t launch_combine_one_kernel(const CombineSendParams& sp, const CombineReduceParams& rp,
-                                      const LaunchCtx& ctx) {
-    const int threads = block_threads(sp.H);
-    const size_t smem = (size_t)(2 * sp.L * sp.R + 1) * sizeof(int);
-    // enough blocks for one token each in the reduce phase; the send phase strides
-    const int want = rp.T > 0 ? rp.T : 1;
-    const int grid = persistent_grid(want, ep_combine_kernel, threads, smem, ctx);
-    return launch("ep_combine", ep_combine_kernel, dim3(grid), dim3(threads), smem, ctx, sp, rp);
+    return launch("ep_dispatch_send_direct", k, dim3(grid), dim3(threads), smem, ctx, p);
 }
 
 cudaError_t launch_combine_invert(const CombineInvertParams& p, const LaunchCtx& ctx) {
@@ -1209,14 +1469,205 @@ cudaError_t launch_combine_invert(const CombineInvertParams& p, const LaunchCtx&
                   ctx, p);
 }
 
-cudaError_t launch_combine_reduce(const CombineReduceParams& p, const LaunchCtx& ctx) {
+cudaError_t launch_direct_combine(const DirectCombineParams& p, const LaunchCtx& ctx) {
     const int threads = block_threads(p.H);
     const bool deep = p.T <= ctx.num_sms;  // one block per SM at most: spend registers on loads in flight
-    auto k = p.direct ? (deep ? ep_combine_reduce_kernel<true, 8> : ep_combine_reduce_kernel<true, 4>)
-                      : (deep ? ep_combine_reduce_kernel<false, 8> : ep_combine_reduce_kernel<false, 4>);
+    auto k = deep ? ep_combine_reduce_direct_kernel<8> : ep_combine_reduce_direct_kernel<4>;
     const int grid = persistent_grid(p.T, k, threads, 0, ctx);
-    return launch(p.direct ? "ep_combine_reduce_direct" : "ep_combine_reduce", k, dim3(grid),
-                  dim3(threads), 0, ctx, p);
+    return launch("ep_combine_reduce_direct", k, dim3(grid), dim3(threads), 0, ctx, p);
+}
+
+// ---- groups -----------------------------------------------------------------------
+namespace {
+
+using DispatchKernel = void (*)(GroupDispatchParams);
+
+template <int kPhases>
+DispatchKernel pick_dispatch(bool fp8, bool fused) {
+    switch ((fp8 ? 2 : 0) | (fused ? 1 : 0)) {
+        case 0: return ep_dispatch_kernel<false, false, kPhases>;
+        case 1: return ep_dispatch_kernel<false, true, kPhases>;
+        case 2: return ep_dispatch_kernel<true, false, kPhases>;
+        default: return ep_dispatch_kernel<true, true, kPhases>;
+    }
+}
+
+size_t dispatch_smem(const GroupDispatchParams& p, bool with_recv) {
+    const size_t n = (size_t)p.E;  // L * R
+    const size_t control = (size_t)(p.fused ? p.E : 0) + 2 * n;
+    const size_t sender = p.fused ? (size_t)p.E : 0;
+    const size_t recv = with_recv ? 2 * n + 1 : 0;
+    size_t m = control > sender ? control : sender;
+    if (recv > m) m = recv;
+    return m * sizeof(int);
+}
+
+}  // namespace
+
+bool group_call_can_be_one_kernel(int T, int K, int E, int num_sms) {
+    // a small batch: one block per token plus the control block, resident at
+    // one block per SM
+    return can_fuse_layout(T, K, E, num_sms) && T + 1 <= num_sms;
+}
+
+cudaError_t launch_group_dispatch(const GroupDispatchParams& p, const LaunchCtx& ctx) {
+    const int threads = block_threads(p.H, 256);
+    const size_t smem = dispatch_smem(p, true);
+    auto k = pick_dispatch<3>(p.use_fp8 != 0, true);
+    const int grid = 1 + (p.T > 0 ? p.T : 1);
+    if (grid > resident_blocks(k, threads, smem, ctx)) return cudaErrorInvalidConfiguration;
+    return launch("ep_dispatch", k, dim3(grid), dim3(threads), smem, ctx, p);
+}
+
+cudaError_t launch_group_dispatch_send(const GroupDispatchParams& p, const LaunchCtx& ctx) {
+    const int threads = block_threads(p.H, 256);
+    const size_t smem = dispatch_smem(p, false);
+    auto k = pick_dispatch<1>(p.use_fp8 != 0, p.fused != 0);
+    // the control block, then one block per token (fused) or a resident wave
+    int senders;
+    if (p.fused) {
+        senders = p.T > 0 ? p.T : 1;
+    } else {
+        long long cap = resident_blocks(k, threads, smem, ctx) - 1;
+        if (cap < 1) cap = 1;
+        senders = (int)(p.T < cap ? (p.T > 0 ? p.T : 1) : cap);
+    }
+    return launch("ep_dispatch_send", k, dim3(1 + senders), dim3(threads), smem, ctx, p);
+}
+
+cudaError_t launch_group_dispatch_recv(const GroupDispatchParams& p, const LaunchCtx& ctx) {
+    const int threads = kRowWarps * 32;
+    const size_t smem = (size_t)(2 * p.E + 1) * sizeof(int);
+    auto k = p.use_fp8 ? ep_dispatch_recv_kernel<true> : ep_dispatch_recv_kernel<false>;
+    // The row count is only known on the device. Under even routing a rank
+    // receives about what it sends; the grid is sized for twice that - blocks
+    // stride, so a skewed or larger load is still covered - and never beyond
+    // one resident wave. Without a row copy the duty is light: fewer blocks.
+    long long rows = 2ll * (p.T * p.K > 64 ? p.T * p.K : 64);
+    const long long worst = (long long)p.E * p.M;
+    if (rows > worst) rows = worst;
+    long long blocks = (rows + kRowWarps - 1) / kRowWarps;
+    if (!p.copy_rows && blocks > 2ll * ctx.num_sms) blocks = 2ll * ctx.num_sms;
+    const int grid = persistent_grid(blocks, k, threads, smem, ctx);
+    return launch("ep_dispatch_recv", k, dim3(grid), dim3(threads), smem, ctx, p);
+}
+
+cudaError_t launch_group_combine(const GroupCombineParams& p, const LaunchCtx& ctx) {
+    const int threads = block_threads(p.H, 256);
+    const size_t smem = (size_t)(2 * p.E + 1) * sizeof(int);
+    auto k = ep_combine_kernel<3>;
+    // one block per token for the reduce duty, and enough blocks for this rank's
+    // share of the publish duty when it has few tokens of its own
+    long long want = p.T > 64 ? p.T : 64;
+    const int grid = persistent_grid(want, k, threads, smem, ctx);
+    return launch("ep_combine", k, dim3(grid), dim3(threads), smem, ctx, p);
+}
+
+cudaError_t launch_group_combine_publish(const GroupCombineParams& p, const LaunchCtx& ctx) {
+    const int threads = kRowWarps * 32;
+    const size_t smem = (size_t)(2 * p.E + 1) * sizeof(int);
+    auto k = ep_combine_kernel<1>;
+    long long blocks = 1;
+    if (!p.zero_copy) {
+        const long long rows = (long long)p.E * p.M;  // L * R * M
+        blocks = (rows + kRowWarps - 1) / kRowWarps;
+    }
+    const int grid = persistent_grid(blocks, k, threads, smem, ctx);
+    return launch("ep_combine_publish", k, dim3(grid), dim3(threads), smem, ctx, p);
+}
+
+cudaError_t launch_group_combine_reduce(const GroupCombineParams& p, const LaunchCtx& ctx) {
+    const int threads = block_threads(p.H);
+    auto k = ep_combine_kernel<2>;
+    const int grid = persistent_grid(p.T, k, threads, 0, ctx);
+    return launch("ep_combine_reduce", k, dim3(grid), dim3(threads), 0, ctx, p);
+}
+
+// ---- in-process groups: all ranks in one cooperative launch ------------------------
+namespace {
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_cooperative(const char* name, void (*kernel)(KArgs...), int grid, int threads,
+                               size_t smem, const LaunchCtx& ctx, Args... args) {
+    (void)name;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, args...);
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
+using DispatchMultiKernel = void (*)(const GroupDispatchParams*, int);
+
+template <int kPhases>
+DispatchMultiKernel pick_dispatch_multi(bool fp8, bool fused) {
+    switch ((fp8 ? 2 : 0) | (fused ? 1 : 0)) {
+        case 0: return ep_dispatch_multi_kernel<false, false, kPhases>;
+        case 1: return ep_dispatch_multi_kernel<false, true, kPhases>;
+        case 2: return ep_dispatch_multi_kernel<true, false, kPhases>;
+        default: return ep_dispatch_multi_kernel<true, true, kPhases>;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_group_dispatch_multi(const GroupDispatchParams* params, int n,
+                                        GroupDispatchParams* dev_params, int phases,
+                                        const LaunchCtx& ctx) {
+    if (n < 1) return cudaSuccess;
+    int want = 2;
+    size_t smem = 0;
+    for (int i = 0; i < n; ++i) {
+        if (params[i].use_fp8 != params[0].use_fp8 || params[i].fused != params[0].fused ||
+            params[i].H != params[0].H)
+            return cudaErrorInvalidValue;
+        const int blocks = 1 + (params[i].T > 0 ? params[i].T : 1);
+        if (blocks > want) want = blocks;
+        const size_t sm = dispatch_smem(params[i], phases == 3);
+        if (sm > smem) smem = sm;
+    }
+    const int threads = block_threads(params[0].H, 256);
+    auto k = phases == 3 ? pick_dispatch_multi<3>(params[0].use_fp8 != 0, params[0].fused != 0)
+                         : pick_dispatch_multi<1>(params[0].use_fp8 != 0, params[0].fused != 0);
+    const long long cap = resident_blocks(k, threads, smem, ctx) / n;
+    if (cap < 2) return cudaErrorInvalidConfiguration;
+    const int per_rank = (int)(want < cap ? want : cap);
+    cudaError_t e = cudaMemcpyAsync(dev_params, params, sizeof(GroupDispatchParams) * n,
+                                    cudaMemcpyHostToDevice, ctx.stream);
+    if (e != cudaSuccess) return e;
+    // (the copy reads pageable host memory: it has been staged when the call returns)
+    return launch_cooperative("ep_dispatch_multi", k, per_rank * n, threads, smem, ctx,
+                              (const GroupDispatchParams*)dev_params, per_rank);
+}
+
+cudaError_t launch_group_combine_multi(const GroupCombineParams* params, int n,
+                                       GroupCombineParams* dev_params, const LaunchCtx& ctx) {
+    if (n < 1) return cudaSuccess;
+    int want = 64;
+    size_t smem = 0;
+    for (int i = 0; i < n; ++i) {
+        if (params[i].H != params[0].H) return cudaErrorInvalidValue;
+        if (params[i].T > want) want = params[i].T;
+        const size_t sm = (size_t)(2 * params[i].E + 1) * sizeof(int);
+        if (sm > smem) smem = sm;
+    }
+    const int threads = block_threads(params[0].H, 256);
+    const long long cap = resident_blocks(ep_combine_multi_kernel, threads, smem, ctx) / n;
+    if (cap < 1) return cudaErrorInvalidConfiguration;
+    const int per_rank = (int)(want < cap ? want : cap);
+    cudaError_t e = cudaMemcpyAsync(dev_params, params, sizeof(GroupCombineParams) * n,
+                                    cudaMemcpyHostToDevice, ctx.stream);
+    if (e != cudaSuccess) return e;
+    return launch_cooperative("ep_combine_multi", ep_combine_multi_kernel, per_rank * n, threads,
+                              smem, ctx, (const GroupCombineParams*)dev_params, per_rank);
 }
 
 }  // namespace mcep

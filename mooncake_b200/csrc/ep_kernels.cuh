@@ -12,13 +12,15 @@ namespace mcep {
 
 constexpr int kMaxTopk = 16;       // MCEP_MAX_TOPK
 constexpr int kMaxRanks = 64;      // ranks of one group (one NVLink domain)
+constexpr int kMaxExperts = 4096;  // MCEP_MAX_EXPERTS
 constexpr int kTileChannels = 512; // one warp pass: 32 lanes x 16 channels
-constexpr int kHeaderBytes = 32;   // staged message header (token index + padding)
+constexpr int kMetaHeaderBytes = 16;  // per-row side message: token index + padding, then scales
 
 // Status bits the kernels may raise instead of trapping.
 constexpr int kStatusSlotRange = 1;
 constexpr int kStatusHardTimeout = 2;
 constexpr int kStatusBadSource = 4;
+constexpr int kStatusNoPeer = 8;  // a rank marked active has no mapped buffer
 
 struct LaunchCtx {
     cudaStream_t stream;
@@ -34,7 +36,6 @@ struct LayoutParams {
     int32_t* slot;            // [T*K]
     int32_t* rank_count;      // [R] or null
     int32_t* expert_prefix;   // [E] or null
-    int32_t* done;            // [E] zeroed here, or null
     unsigned* ticket;         // scratch word, required with rank_count/expert_prefix
     // single-rank groups: the layout already is the receive layout
     int32_t* recv_count;      // [E] or null
@@ -42,76 +43,25 @@ struct LayoutParams {
 };
 cudaError_t launch_layout(const LayoutParams& p, const LaunchCtx& ctx);
 
-// ---- dispatch ---------------------------------------------------------------
-struct DispatchSendParams {
+// ---- single rank: packed outputs written directly ------------------------------
+struct DirectDispatchParams {
     const void* x;              // [T][H] bf16
     const int64_t* topk_idx;    // [T][K]
-    const int32_t* slot;        // [T*K] from the layout kernel
-    const int32_t* count;       // [E]
-    int32_t* done;              // [E] completion counters (zero on entry)
-    const int32_t* active_ranks;
-    void* const* peer_base;     // [R] base of every rank's symmetric buffer
-    int T, K, E, R, M, H, rank;
+    const int32_t* slot;        // [T*K] from the layout kernel (not fused)
+    const int32_t* count;       // [E]   from the layout kernel (not fused)
+    int T, K, E, M, H;
     int use_fp8;
     int fused;                  // count the slots here (slot/count unused) - small batches
-    size_t stage_off;           // dispatch staging of this call's parity
-    size_t flag_off;            // dispatch flags of this call's parity
-    size_t msg_stride;
-    uint32_t seq;
     int32_t* status;
-    // direct mode (single rank): write the packed outputs, no staging, no flags
-    int direct;
     void* recv_x;
     float* recv_scales;
     int32_t* recv_src_info;
-    int32_t* recv_count;        // direct + fused: [E]
-    int64_t* layout_range;      // direct + fused: [E]
+    int32_t* recv_count;        // fused: [E]
+    int64_t* layout_range;      // fused: [E]
 };
-// whether the send kernel may count the slots itself for this problem size
-bool dispatch_send_can_fuse_layout(int T, int K, int H, int num_sms);
-cudaError_t launch_dispatch_send(const DispatchSendParams& p, const LaunchCtx& ctx);
-
-// How a receive kernel waits for flags (see resolve_flag in ep_kernels.cu).
-struct WaitSpec {
-    const uint64_t* flags;      // local flags of this call's parity and direction
-    uint64_t* resolved;         // scratch, one word per flag: the verdict for this call
-    int32_t* active_ranks;
-    uint32_t seq;
-    int64_t timeout_ns;         // < 0: only the hard bound applies
-    int64_t hard_timeout_ns;
-    int32_t* status;
-};
-
-struct DispatchRecvParams {
-    WaitSpec w;                 // flags indexed expert * R + source
-    const char* stage;          // local dispatch staging of this parity
-    int L, R, M, H;
-    int use_fp8;
-    int expected_rows;          // host's estimate of the rows this rank receives (grid sizing)
-    size_t msg_stride;
-    void* recv_x;
-    float* recv_scales;
-    int32_t* recv_src_info;
-    int32_t* recv_count;        // [L]
-    int64_t* layout_range;      // [L][R]
-};
-cudaError_t launch_dispatch_recv(const DispatchRecvParams& p, const LaunchCtx& ctx);
-
-// ---- combine ----------------------------------------------------------------
-struct CombineSendParams {
-    const void* x;              // [L][R*M][H] bf16
-    const int32_t* src_info;    // [L][R*M]
-    const int64_t* layout_range;// [L][R]
-    const int32_t* active_ranks;
-    void* const* peer_base;
-    int32_t* done;              // [L*R] completion counters (zero on entry, zero on exit)
-    int L, R, M, H, rank;
-    size_t stage_off;           // combine staging of this parity
-    size_t flag_off;            // combine flags of this parity
-    uint32_t seq;
-    int32_t* status;
-};
-cudaError_t launch_combine_send(const CombineSendParams& p, const LaunchCtx& ctx);
+// whether a send kernel may count the slots itself for this problem size
+bool can_fuse_layout(int T, int K, int E, int num_sms);
+cudaError_t launch_direct_dispatch(const DirectDispatchParams& p, const LaunchCtx& ctx);
 
 // Single rank: (token, k) -> packed row, inverted from the handle.
 struct CombineInvertParams {
@@ -124,34 +74,116 @@ struct CombineInvertParams {
 };
 cudaError_t launch_combine_invert(const CombineInvertParams& p, const LaunchCtx& ctx);
 
-struct CombineReduceParams {
+struct DirectCombineParams {
     const int64_t* topk_idx;    // [T][K]
     const float* topk_weights;  // [T][K]
     const int32_t* active_ranks;
-    int T, K, E, L, M, H;
-    // staged: waits for each needed expert's flag (w.flags indexed by global
-    // expert), then reads rows at stage + (expert * M + token) * 2H
-    WaitSpec w;
-    const char* stage;
-    // direct: rows at x + (expert * R*M + rowmap[t*K+k]) * 2H (single rank)
-    int direct;
-    const void* x;
+    int T, K, E, M, H;
+    const void* x;              // rows at x + (expert * M + rowmap[t*K+k]) * 2H
     const int32_t* rowmap;
-    int RM;
-    // direct + search: no rowmap; rows are looked up in the handle by the kernel
+    // search: no rowmap; rows are looked up in the handle by the kernel
     int search;
     const int32_t* src_info;
     const int64_t* layout_range;
     void* combined_x;           // [T][H] bf16
 };
-cudaError_t launch_combine_reduce(const CombineReduceParams& p, const LaunchCtx& ctx);
+cudaError_t launch_direct_combine(const DirectCombineParams& p, const LaunchCtx& ctx);
 
-// Both phases of a call in one launch (small batches in a group, no hook).
-bool call_can_be_one_kernel(int T, int K, int H, int num_sms);
-cudaError_t launch_dispatch_one_kernel(const DispatchSendParams& sp, const DispatchRecvParams& rp,
-                                       const LaunchCtx& ctx);
-cudaError_t launch_combine_one_kernel(const CombineSendParams& sp, const CombineReduceParams& rp,
-                                      const LaunchCtx& ctx);
+// ---- groups: words exchanged through symmetric memory -----------------------------
+// All words are 64-bit: (sequence number of the call << 32) | value, value >= 1.
+// A word that does not carry the current sequence number has not arrived.
+struct Words {
+    // byte offsets inside every rank's symmetric allocation, for this call's parity
+    size_t cnt_off;    // at the owner of an expert: [R src][L] tokens src sends to local expert
+    size_t beg_off;    // at a sender: [E] first row of its segment in expert e, written by e's owner
+    size_t dflag_off;  // at a receiver: [R src] all of src's dispatch rows have landed
+    size_t cflag_off;  // at a token owner: [R owner] owner's expert outputs can be read
+};
+
+struct WaitCfg {
+    int32_t* active_ranks;     // read and written (timeout -> 0)
+    int64_t timeout_ns;        // < 0: only the hard bound applies
+    int64_t hard_timeout_ns;
+    int32_t* status;
+};
+
+// Dispatch in a group. Block 0 is the control block: it publishes this rank's
+// per-expert counts to the experts' owners, collects the counts all sources
+// announce for its own experts, fixes the receive layout and answers every
+// source with the first row of its segment. The other blocks send token rows
+// straight to their final place in the owners' packed receive area.
+struct GroupDispatchParams {
+    const void* x;              // [T][H] bf16
+    const int64_t* topk_idx;    // [T][K]
+    const int32_t* slot;        // [T*K] from the layout kernel (not fused)
+    const int32_t* count;       // [E]   from the layout kernel (not fused)
+    void* const* peer_base;     // [R] base of every rank's symmetric buffer
+    char* local_base;           // this rank's
+    int T, K, E, R, M, H, rank;
+    int use_fp8;
+    int fused;
+    Words w;
+    size_t rx_off;              // packed receive rows [L][R*M][row_bytes] of this parity
+    size_t meta_off;            // side messages [L][R*M][meta_stride] of this parity
+    int row_bytes, meta_stride;
+    uint32_t seq;
+    WaitCfg wait;
+    // scratch in the local workspace (per parity)
+    uint64_t* res_cnt;          // [L*R] the control block's verdict per (expert, source)
+    uint64_t* res_dflag;        // [R] verdict words of the payload flags
+    unsigned* ticket;           // sender blocks that have finished
+    int32_t* rowmap;            // [T*K] row of (token, k) at its expert's owner, kept for combine
+    // outputs (caller's tensors)
+    void* recv_x;               // == local_base + rx_off when the caller took the in-place tensor
+    float* recv_scales;
+    int32_t* recv_src_info;
+    int32_t* recv_count;        // [L]
+    int64_t* layout_range;      // [L][R]
+    int copy_rows;              // recv_x is a tensor of the caller's: copy the rows out
+};
+bool group_call_can_be_one_kernel(int T, int K, int E, int num_sms);
+// one launch: control + send + receive duties
+cudaError_t launch_group_dispatch(const GroupDispatchParams& p, const LaunchCtx& ctx);
+// two launches (hook mode, large batches, caller-owned recv_x)
+cudaError_t launch_group_dispatch_send(const GroupDispatchParams& p, const LaunchCtx& ctx);
+cudaError_t launch_group_dispatch_recv(const GroupDispatchParams& p, const LaunchCtx& ctx);
+
+// Combine in a group: expert outputs are made readable in symmetric memory
+// (copied there, or written there by the caller: zero copy), every peer is told
+// so with one word, and token owners read their rows straight from the experts'
+// owners and reduce them.
+struct GroupCombineParams {
+    const void* x;              // [L][R*M][H] bf16 expert outputs (ignored with zero_copy)
+    const int64_t* layout_range;// [L][R] from the handle
+    const int64_t* topk_idx;    // [T][K]
+    const float* topk_weights;  // [T][K]
+    const int32_t* rowmap;      // [T*K] left by the dispatch call of this handle
+    void* const* peer_base;
+    char* local_base;
+    int T, K, E, R, M, H, rank;
+    int zero_copy;
+    Words w;
+    size_t cin_off;             // combine input [L][R*M][H] bf16 of this parity
+    uint32_t seq;
+    WaitCfg wait;
+    uint64_t* res_cflag;        // [R]
+    unsigned* ticket;
+    void* combined_x;           // [T][H] bf16
+};
+cudaError_t launch_group_combine(const GroupCombineParams& p, const LaunchCtx& ctx);
+cudaError_t launch_group_combine_publish(const GroupCombineParams& p, const LaunchCtx& ctx);
+cudaError_t launch_group_combine_reduce(const GroupCombineParams& p, const LaunchCtx& ctx);
+
+// In-process groups (several logical ranks on one GPU, tests): the send phase
+// (phases = 1) or the whole call (phases = 3) of `n` ranks as ONE cooperative
+// launch, because kernels that wait for one another must not be separate
+// launches on one GPU. `dev_params` is device memory for `n` parameter blocks.
+// All ranks must agree on payload type, hidden size and `fused`.
+cudaError_t launch_group_dispatch_multi(const GroupDispatchParams* params, int n,
+                                        GroupDispatchParams* dev_params, int phases,
+                                        const LaunchCtx& ctx);
+cudaError_t launch_group_combine_multi(const GroupCombineParams* params, int n,
+                                       GroupCombineParams* dev_params, const LaunchCtx& ctx);
 
 uint64_t kernel_launch_count();
 // Per-kernel device times: switch on, run, then drain "name launches total_ms" lines.

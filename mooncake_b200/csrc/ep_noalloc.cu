@@ -10,7 +10,7 @@
 //
 // `mcep_combine_single_rank_static` is that case with its scratch - the
 // (token, k) -> packed-row map that `ep_combine_invert_kernel` fills and
-// `ep_combine_reduce_kernel` reads - in a file-scope device array instead of a
+// `ep_combine_reduce_direct_kernel` reads - in a file-scope device array instead of a
 // cudaMalloc'ed workspace. It calls no cudaMalloc, cudaFree or allocating
 // library routine. The array is part of the library image: every GPU that loads
 // libmcep.so holds it until the process exits.
@@ -124,11 +124,41 @@ extern "C" int mcep_combine_single_rank_static(const void* x, const int64_t* top
     ip.rowmap = rowmap, ip.status = status;
     STATIC_CUDA(mcep::launch_combine_invert(ip, ctx));
 
-    mcep::CombineReduceParams rp = {};
+    mcep::DirectCombineParams rp = {};
     rp.topk_idx = topk_idx, rp.topk_weights = topk_weights, rp.active_ranks = active;
-    rp.T = T, rp.K = K, rp.E = E, rp.L = E, rp.M = M, rp.H = H;
-    rp.stage = nullptr, rp.direct = 1, rp.x = x, rp.rowmap = rowmap, rp.RM = M;
+    rp.T = T, rp.K = K, rp.E = E, rp.M = M, rp.H = H;
+    rp.x = x, rp.rowmap = rowmap, rp.search = 0;
+    rp.src_info = src_info, rp.layout_range = layout_range;
     rp.combined_x = combined_x;
-    STATIC_CUDA(mcep::launch_combine_reduce(rp, ctx));
+    STATIC_CUDA(mcep::launch_direct_combine(rp, ctx));
+    return MCEP_OK;
+}
+
+// The kernels record anomalies of the handle they were given (a row or a token
+// index out of range) in a word of the static array instead of trapping. This
+// reads that word for the current device and clears it; like the entry point
+// above it allocates nothing. A call that has not run on this device yet reads
+// as 0.
+extern "C" int mcep_static_status(int32_t* out) {
+    g_static_error[0] = 0;
+    if (out == nullptr) STATIC_FAIL(MCEP_ERR_INVALID, "Failed: Assertion error: null output pointer");
+    *out = 0;
+    int dev = 0;
+    STATIC_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) STATIC_FAIL(MCEP_ERR_INVALID, "Failed: device index %d", dev);
+    DeviceSetup setup;
+    {
+        std::lock_guard<std::mutex> lk(g_setup_mu);
+        setup = g_setup[dev];
+    }
+    if (!setup.ready) return MCEP_OK;
+    // plain cudaMemcpy: ordered after the kernels of earlier calls on any
+    // blocking stream; callers on non-blocking streams synchronise first
+    STATIC_CUDA(cudaDeviceSynchronize());
+    STATIC_CUDA(cudaMemcpy(out, setup.scratch + 64, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    if (*out != 0) {
+        const int32_t zero = 0;
+        STATIC_CUDA(cudaMemcpy(setup.scratch + 64, &zero, sizeof(zero), cudaMemcpyHostToDevice));
+    }
     return MCEP_OK;
 }

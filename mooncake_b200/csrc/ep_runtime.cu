@@ -48,10 +48,18 @@ int fail(int code, const char* fmt, ...) {
     } while (0)
 
 constexpr size_t kWorkspaceBytes = 32u << 20;  // as NUM_WORKSPACE_BYTES in the reference
-// Front of the symmetric allocation, ahead of the caller-sized data area:
-// flags[parity 2][direction 2][MCEP_MAX_EXPERTS] u64.
-constexpr size_t kFlagBlock = (size_t)MCEP_MAX_EXPERTS * sizeof(uint64_t);
-constexpr size_t kHeaderRegion = 4 * kFlagBlock;
+// Front of the symmetric allocation, ahead of the caller-sized data area: the
+// words ranks write into each other's memory, twice (one set per parity):
+//   cnt   [MCEP_MAX_EXPERTS] u64   counts announced to this rank (owner side)
+//   beg   [MCEP_MAX_EXPERTS] u64   first rows answered to this rank (sender side)
+//   dflag [64] u64, cflag [64] u64 payload / combine-input words
+// and, at the very end, the two call counters this rank last published (read
+// by its peers when the group's membership is refreshed).
+constexpr size_t kWordBlock = (size_t)MCEP_MAX_EXPERTS * sizeof(uint64_t);
+constexpr size_t kHeaderParity = 128u << 10;
+constexpr size_t kHeaderRegion = 2 * kHeaderParity;
+constexpr size_t kPubSeqOff = kHeaderRegion - 256;
+static_assert(2 * kWordBlock + 2 * 64 * sizeof(uint64_t) <= kHeaderParity - 256, "header layout");
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -84,25 +92,48 @@ struct mcep_buffer {
     std::vector<void*> ipc_opened;   // mappings to close
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ev_a = nullptr, ev_b = nullptr;  // reusable ordering events
-    uint32_t seq = 0;                // calls issued so far (dispatch + combine)
+    uint32_t dseq = 0, cseq = 0;     // dispatch / combine calls issued so far
 
     // workspace carve-up (per parity so two calls in flight do not share scratch)
     struct Scratch {
-        int32_t *slot, *count, *done, *cdone, *rowmap;
-        uint64_t *dres, *cres;  // verdict words of the receive kernels
-        unsigned* ticket;
+        int32_t *slot, *count, *rowmap;
+        uint64_t *res_cnt, *res_dflag, *res_cflag;  // verdict words
+        unsigned *layout_ticket, *send_ticket, *publish_ticket;
     } scratch[2];
     size_t scratch_entries = 0;  // capacity of slot/rowmap in int32
+
+    // In-process groups: calls are prepared but not launched until
+    // mcep_launch_deferred starts all ranks' work in one launch.
+    bool defer = false;
+    struct Pending {
+        int kind = 0;                // 0 none, 1 dispatch, 2 combine
+        int phases = 0;              // dispatch: 1 send / 3 send + receive; combine: 1 publish / 3 both
+        bool then_second = false;    // launch the second phase right after (no hook was asked for)
+        cudaStream_t stream = nullptr;
+        mcep::GroupDispatchParams d;
+        mcep::GroupCombineParams c;
+    } pending;
+
+    // what combine needs to know about the dispatch call a handle came from
+    struct DispatchRecord {
+        const void* key = nullptr;  // the handle's src_info tensor
+        uint32_t seq = 0;
+        int T = 0, K = 0, E = 0, M = 0, H = 0;
+    } record[2];
 };
 
 namespace {
 
+// Data area of one parity: [dispatch area | combine input].
+//   dispatch area  E*M*(32 + 2H) bytes: receive rows [L][R*M][H or 2H], then the
+//                  side messages [L][R*M][meta_stride]
+//   combine input  [L][R*M][2H]
+// Twice that never exceeds the reference's size hint 16E + 4*E*M*(32 + 2H).
 struct Geometry {
     int L, RM, ntiles;
-    size_t msg_stride;      // staged dispatch message
-    size_t dstage_bytes;    // one parity's dispatch staging
-    size_t cstage_bytes;    // one parity's combine staging
-    size_t parity_bytes;
+    int row_bytes, meta_stride;
+    size_t darea_bytes, cin_bytes, parity_bytes;
+    size_t meta_off;  // inside the dispatch area
 };
 
 Geometry geometry(int R, int E, int M, int H, bool fp8) {
@@ -110,12 +141,12 @@ Geometry geometry(int R, int E, int M, int H, bool fp8) {
     g.L = E / R;
     g.RM = R * M;
     g.ntiles = (H + mcep::kTileChannels - 1) / mcep::kTileChannels;
-    // sized for the larger (bf16) message so the carve-up does not depend on the mode
-    (void)fp8;
-    g.msg_stride = align_up((size_t)mcep::kHeaderBytes + 2 * (size_t)H, 32);
-    g.dstage_bytes = (size_t)E * M * g.msg_stride;
-    g.cstage_bytes = (size_t)E * M * 2 * (size_t)H;
-    g.parity_bytes = g.dstage_bytes + g.cstage_bytes;
+    g.row_bytes = H * (fp8 ? 1 : 2);
+    g.meta_stride = mcep::kMetaHeaderBytes + (fp8 ? 16 * g.ntiles : 0);
+    g.darea_bytes = (size_t)E * M * (32 + 2 * (size_t)H);
+    g.cin_bytes = (size_t)E * M * 2 * (size_t)H;
+    g.parity_bytes = g.darea_bytes + g.cin_bytes;
+    g.meta_off = (size_t)E * M * g.row_bytes;
     return g;
 }
 
@@ -214,20 +245,23 @@ int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int
 #undef CK
     // workspace: [status 256 B][parity 0 scratch][parity 1 scratch]
     b->status = reinterpret_cast<int32_t*>(b->workspace);
+    const size_t words = (size_t)MCEP_MAX_EXPERTS * sizeof(uint64_t);
     const size_t small = (size_t)(MCEP_MAX_EXPERTS + 64) * sizeof(int32_t);
     const size_t half = (kWorkspaceBytes - 256) / 2;
-    const size_t big = (half - 7 * small - 256) / 2;  // bytes for each of slot / rowmap
+    const size_t fixed = 256 + small + words + 2 * 64 * sizeof(uint64_t);
+    const size_t big = (half - fixed - 512) / 2;  // bytes for each of slot / rowmap
     b->scratch_entries = big / sizeof(int32_t);
     for (int par = 0; par < 2; ++par) {
         char* w = b->workspace + 256 + par * half;
         auto& s = b->scratch[par];
-        s.ticket = reinterpret_cast<unsigned*>(w);
+        s.layout_ticket = reinterpret_cast<unsigned*>(w);
+        s.send_ticket = reinterpret_cast<unsigned*>(w + 64);
+        s.publish_ticket = reinterpret_cast<unsigned*>(w + 128);
         w += 256;
         s.count = reinterpret_cast<int32_t*>(w), w += small;
-        s.done = reinterpret_cast<int32_t*>(w), w += small;
-        s.dres = reinterpret_cast<uint64_t*>(w), w += 2 * small;
-        s.cres = reinterpret_cast<uint64_t*>(w), w += 2 * small;
-        s.cdone = reinterpret_cast<int32_t*>(w), w += small;
+        s.res_cnt = reinterpret_cast<uint64_t*>(w), w += words;
+        s.res_dflag = reinterpret_cast<uint64_t*>(w), w += 64 * sizeof(uint64_t);
+        s.res_cflag = reinterpret_cast<uint64_t*>(w), w += 64 * sizeof(uint64_t);
         s.slot = reinterpret_cast<int32_t*>(w), w += big / 256 * 256;
         s.rowmap = reinterpret_cast<int32_t*>(w);
     }
@@ -262,6 +296,38 @@ int mcep_buffer_p2p_enabled(const mcep_buffer* b) { return b && b->p2p_enabled ?
 int mcep_buffer_is_roce(const mcep_buffer*) { return 0; }
 int mcep_buffer_use_fast_path(const mcep_buffer* b) { return b && b->all_peers ? 1 : 0; }
 
+// The words ranks exchange carry the number of the call they belong to, so all
+// ranks of a group must count their calls alike. A rank that sat out some calls
+// (masked out, or re-created from scratch) is brought back in step when the
+// membership is refreshed: every rank leaves its two counters in its own
+// symmetric memory before the handles are exchanged, reads every mapped peer's
+// afterwards and continues from the largest.
+static int publish_seq(mcep_buffer* b) {
+    const uint32_t pub[2] = {b->dseq, b->cseq};
+    MCEP_CUDA(cudaMemcpy(b->base + kPubSeqOff, pub, sizeof(pub), cudaMemcpyHostToDevice));
+    return MCEP_OK;
+}
+
+static int adopt_largest_seq(mcep_buffer* b) {
+    uint32_t d = b->dseq, c = b->cseq;
+    for (int r = 0; r < b->num_ranks; ++r) {
+        if (r == b->rank || !b->available[r] || b->peer_host[r] == nullptr) continue;
+        uint32_t pub[2] = {0, 0};
+        MCEP_CUDA(cudaMemcpy(pub, static_cast<char*>(b->peer_host[r]) + kPubSeqOff, sizeof(pub),
+                             cudaMemcpyDeviceToHost));
+        if (pub[0] > d) d = pub[0];
+        if (pub[1] > c) c = pub[1];
+    }
+    if (d != b->dseq || c != b->cseq) {
+        // handles of calls made before the jump no longer name a known call
+        b->record[0] = mcep_buffer::DispatchRecord();
+        b->record[1] = mcep_buffer::DispatchRecord();
+    }
+    b->dseq = d;
+    b->cseq = c;
+    return MCEP_OK;
+}
+
 int mcep_buffer_get_ipc_handle(mcep_buffer* b, int32_t* out, int capacity, int* n_written) {
     MCEP_REQUIRE(b != nullptr && n_written != nullptr);
     *n_written = 0;
@@ -269,6 +335,8 @@ int mcep_buffer_get_ipc_handle(mcep_buffer* b, int32_t* out, int capacity, int* 
     MCEP_REQUIRE(out != nullptr && capacity >= MCEP_IPC_HANDLE_INT32S);
     static_assert(sizeof(cudaIpcMemHandle_t) == MCEP_IPC_HANDLE_INT32S * sizeof(int32_t),
                   "handle size");
+    MCEP_CUDA(cudaDeviceSynchronize());
+    if (int rc = publish_seq(b)) return rc;
     cudaIpcMemHandle_t h;
     MCEP_CUDA(cudaIpcGetMemHandle(&h, b->base));
     std::memcpy(out, &h, sizeof(h));
@@ -284,7 +352,7 @@ static int publish_peers(mcep_buffer* b, const int32_t* mask) {
         if (mask && mask[r] == 0) continue;
         if (!b->available[r] || b->peer_host[r] == nullptr) b->all_peers = false;
     }
-    return MCEP_OK;
+    return adopt_largest_seq(b);
 }
 
 int mcep_buffer_sync_nvlink_ipc_handles(mcep_buffer* b, const int32_t* handles, int n_per_handle,
@@ -295,11 +363,34 @@ int mcep_buffer_sync_nvlink_ipc_handles(mcep_buffer* b, const int32_t* handles, 
     MCEP_CUDA(cudaDeviceSynchronize());
     for (void* p : b->ipc_opened) cudaIpcCloseMemHandle(p);
     b->ipc_opened.clear();
+    int device_count = 1;
+    if (cudaGetDeviceCount(&device_count) != cudaSuccess || device_count < 1) {
+        cudaGetLastError();
+        device_count = 1;
+    }
     for (int r = 0; r < b->num_ranks; ++r) {
         if (r == b->rank) continue;
         b->peer_host[r] = nullptr;
         b->available[r] = 0;
         if (mask && mask[r] == 0) continue;
+        // Rank r runs on device r % device_count of this node (the placement the
+        // reference assumes, p2p_device_transport.cpp:591-604): ask the driver
+        // whether that device can be reached before mapping its memory. With one
+        // visible device per process the question cannot be asked; the mapping
+        // call below then decides.
+        const int dst_device = r % device_count;
+        if (dst_device != b->device) {
+            int can_access = 0;
+            if (cudaDeviceCanAccessPeer(&can_access, b->device, dst_device) != cudaSuccess) {
+                cudaGetLastError();
+                can_access = 0;
+            }
+            if (!can_access) {
+                fprintf(stderr, "[mcep] [EP P2P] rank %d (device %d) -> rank %d (device %d): "
+                                "canAccessPeer=0\n", b->rank, b->device, r, dst_device);
+                continue;
+            }
+        }
         cudaIpcMemHandle_t h;
         std::memcpy(&h, handles + (size_t)r * n_per_handle, sizeof(h));
         void* p = nullptr;
@@ -320,15 +411,19 @@ int mcep_buffer_sync_nvlink_ipc_handles(mcep_buffer* b, const int32_t* handles, 
 int mcep_buffer_local_base(mcep_buffer* b, void** base) {
     MCEP_REQUIRE(b != nullptr && base != nullptr);
     *base = b->base;
-    return MCEP_OK;
+    // in-process groups exchange base pointers instead of handles: this is the
+    // moment a rank leaves its call counters for its peers
+    MCEP_CUDA(cudaDeviceSynchronize());
+    return publish_seq(b);
 }
 
 int mcep_buffer_set_peer_bases(mcep_buffer* b, void* const* bases, const int32_t* available) {
     MCEP_REQUIRE(b != nullptr && bases != nullptr);
+    MCEP_CUDA(cudaDeviceSynchronize());
     for (int r = 0; r < b->num_ranks; ++r) {
         if (r == b->rank) continue;
-        b->peer_host[r] = bases[r];
         b->available[r] = (available ? available[r] : 1) && bases[r] != nullptr;
+        b->peer_host[r] = b->available[r] ? bases[r] : nullptr;  // an unavailable rank is never mapped
     }
     return publish_peers(b, available);
 }
@@ -346,6 +441,8 @@ int mcep_buffer_set_option(mcep_buffer* b, const char* name, int64_t value) {
         b->fuse_layout = value != 0;
     } else if (!std::strcmp(name, "one_kernel")) {
         b->one_kernel = value != 0;
+    } else if (!std::strcmp(name, "defer_launch")) {
+        b->defer = value != 0;
     } else {
         return fail(MCEP_ERR_INVALID, "Failed: unknown option '%s'", name);
     }
@@ -355,6 +452,69 @@ int mcep_buffer_set_option(mcep_buffer* b, const char* name, int64_t value) {
 int mcep_buffer_status(mcep_buffer* b, int32_t* out, int n) {
     MCEP_REQUIRE(b != nullptr && out != nullptr && n >= 1 && n <= 64);
     MCEP_CUDA(cudaMemcpy(out, b->status, sizeof(int32_t) * n, cudaMemcpyDeviceToHost));
+    return MCEP_OK;
+}
+
+int mcep_buffer_call_counts(const mcep_buffer* b, uint32_t* dispatch_calls, uint32_t* combine_calls) {
+    MCEP_REQUIRE(b != nullptr && dispatch_calls != nullptr && combine_calls != nullptr);
+    *dispatch_calls = b->dseq;
+    *combine_calls = b->cseq;
+    return MCEP_OK;
+}
+
+static bool is_group(const mcep_buffer* b) { return b->num_ranks > 1 || b->force_staged; }
+
+int mcep_buffer_next_recv_x(mcep_buffer* b, int M, int hidden, int num_experts, int use_fp8,
+                            void** out, size_t* bytes) {
+    MCEP_REQUIRE(b != nullptr && out != nullptr);
+    *out = nullptr;
+    if (bytes) *bytes = 0;
+    if (!is_group(b)) return MCEP_OK;  // a single rank writes the caller's tensor directly
+    MCEP_REQUIRE(num_experts > 0 && num_experts % b->num_ranks == 0 && M > 0 && hidden > 0);
+    const Geometry g = geometry(b->num_ranks, num_experts, M, hidden, use_fp8 != 0);
+    if (2 * g.parity_bytes > (size_t)b->num_bytes) return MCEP_OK;  // dispatch will report it
+    const int par = (b->dseq + 1) & 1;
+    *out = b->base + kHeaderRegion + (size_t)par * g.parity_bytes;
+    if (bytes) *bytes = (size_t)num_experts * M * g.row_bytes;
+    return MCEP_OK;
+}
+
+int mcep_buffer_next_combine_buffer(mcep_buffer* b, int M, int hidden, int num_experts, void** out,
+                                    size_t* bytes) {
+    MCEP_REQUIRE(b != nullptr && out != nullptr);
+    *out = nullptr;
+    if (bytes) *bytes = 0;
+    if (!is_group(b)) return MCEP_OK;  // a single rank reads the caller's tensor directly
+    MCEP_REQUIRE(num_experts > 0 && num_experts % b->num_ranks == 0 && M > 0 && hidden > 0);
+    const Geometry g = geometry(b->num_ranks, num_experts, M, hidden, false);
+    if (2 * g.parity_bytes > (size_t)b->num_bytes)
+        return fail(MCEP_ERR_INVALID,
+                    "Failed: Assertion error %s:%d 'layout.total_bytes <= num_ep_buffer_bytes' "
+                    "(need %zu, have %lld)",
+                    __FILE__, __LINE__, 2 * g.parity_bytes, (long long)b->num_bytes);
+    const int par = (b->cseq + 1) & 1;
+    *out = b->base + kHeaderRegion + (size_t)par * g.parity_bytes + g.darea_bytes;
+    if (bytes) *bytes = g.cin_bytes;
+    return MCEP_OK;
+}
+
+static mcep::Words words_of(int dpar, int cpar) {
+    mcep::Words w;
+    w.cnt_off = (size_t)dpar * kHeaderParity;
+    w.beg_off = w.cnt_off + kWordBlock;
+    w.dflag_off = w.beg_off + kWordBlock;
+    w.cflag_off = (size_t)cpar * kHeaderParity + 2 * kWordBlock + 64 * sizeof(uint64_t);
+    return w;
+}
+
+static int completion_event(cudaStream_t stream, mcep_event** out_event) {
+    auto* ev = new mcep_event();
+    if (cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventRecord(ev->ev, stream) != cudaSuccess) {
+        delete ev;
+        return fail(MCEP_ERR_CUDA, "Failed: CUDA error creating the completion event");
+    }
+    *out_event = ev;
     return MCEP_OK;
 }
 
@@ -387,19 +547,17 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     if (int rc = check_connected(b)) return rc;
 
     const bool fp8 = a->use_fp8 != 0;
-    const bool direct = (R == 1) && !b->force_staged;
+    const bool group = is_group(b);
     const Geometry g = geometry(R, E, M, H, fp8);
-    if (!direct && 2 * g.parity_bytes > (size_t)b->num_bytes)
+    if (group && 2 * g.parity_bytes > (size_t)b->num_bytes)
         return fail(MCEP_ERR_INVALID,
                     "Failed: Assertion error %s:%d 'layout.total_bytes <= num_ep_buffer_bytes' "
                     "(need %zu, have %lld)",
                     __FILE__, __LINE__, 2 * g.parity_bytes, (long long)b->num_bytes);
 
-    const uint32_t seq = ++b->seq;
+    const uint32_t seq = ++b->dseq;
     const int par = seq & 1;
     auto& sc = b->scratch[par];
-    const size_t data0 = kHeaderRegion + (size_t)par * g.parity_bytes;
-    const size_t dflag_off = (size_t)(par * 2 + 0) * kFlagBlock;
 
     cudaStream_t compute = reinterpret_cast<cudaStream_t>(a->compute_stream);
     // Without a hook or an event the caller's stream has to wait for the result
@@ -412,66 +570,98 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     mcep::LaunchCtx first{stream, b->num_sms, false};
     mcep::LaunchCtx next{stream, b->num_sms, b->pdl};
 
-    // (the in-kernel layout keeps three E-sized tables in shared memory)
-    const bool fused = mcep::dispatch_send_can_fuse_layout(T, K, H, b->num_sms) && b->fuse_layout &&
-                       E <= 2048;
+    const bool fused = mcep::can_fuse_layout(T, K, E, b->num_sms) && b->fuse_layout;
     if (!fused) {
         mcep::LayoutParams lp = {};
         lp.topk_idx = a->topk_idx;
         lp.T = T, lp.K = K, lp.E = E, lp.R = R;
-        lp.count = sc.count, lp.slot = sc.slot, lp.done = sc.done, lp.ticket = sc.ticket;
-        if (direct) {
+        lp.count = sc.count, lp.slot = sc.slot, lp.ticket = sc.layout_ticket;
+        if (!group) {
             lp.recv_count = a->packed_recv_count;
             lp.layout_range = a->packed_recv_layout_range;
         }
         MCEP_CUDA(mcep::launch_layout(lp, first));
     }
 
-    mcep::DispatchSendParams sp = {};
-    sp.x = a->x, sp.topk_idx = a->topk_idx, sp.slot = sc.slot, sp.count = sc.count;
-    sp.done = sc.done, sp.active_ranks = a->active_ranks, sp.peer_base = b->peer_dev;
-    sp.T = T, sp.K = K, sp.E = E, sp.R = R, sp.M = M, sp.H = H, sp.rank = b->rank;
-    sp.use_fp8 = fp8, sp.fused = fused;
-    sp.stage_off = data0, sp.flag_off = dflag_off, sp.msg_stride = g.msg_stride;
-    sp.seq = seq, sp.status = b->status;
-    sp.direct = direct, sp.recv_x = a->packed_recv_x, sp.recv_scales = a->packed_recv_x_scales;
-    sp.recv_src_info = a->packed_recv_src_info;
-    sp.recv_count = a->packed_recv_count, sp.layout_range = a->packed_recv_layout_range;
+    if (!group) {
+        // a single rank: the packed outputs are written directly, no words, no waits
+        mcep::DirectDispatchParams dp = {};
+        dp.x = a->x, dp.topk_idx = a->topk_idx, dp.slot = sc.slot, dp.count = sc.count;
+        dp.T = T, dp.K = K, dp.E = E, dp.M = M, dp.H = H, dp.use_fp8 = fp8, dp.fused = fused;
+        dp.status = b->status, dp.recv_x = a->packed_recv_x;
+        dp.recv_scales = a->packed_recv_x_scales, dp.recv_src_info = a->packed_recv_src_info;
+        dp.recv_count = a->packed_recv_count, dp.layout_range = a->packed_recv_layout_range;
+        MCEP_CUDA(mcep::launch_direct_dispatch(dp, fused ? first : next));
+        if (a->return_recv_hook) {
+            auto* h = new mcep_hook();
+            h->fn = []() { return MCEP_OK; };
+            *out_hook = h;
+            return MCEP_OK;
+        }
+        if (a->async_finish) return completion_event(stream, out_event);
+        return MCEP_OK;
+    }
 
-    // receive phase, now or from the hook
-    mcep::DispatchRecvParams pp = {};
-    pp.w.flags = reinterpret_cast<const uint64_t*>(b->base + dflag_off);
-    pp.w.resolved = sc.dres, pp.w.active_ranks = a->active_ranks, pp.w.seq = seq;
-    pp.w.timeout_ns = to_ns(a->timeout_us), pp.w.hard_timeout_ns = b->hard_timeout_ns;
-    pp.w.status = b->status;
-    pp.stage = b->base + data0;
-    pp.L = g.L, pp.R = R, pp.M = M, pp.H = H, pp.use_fp8 = fp8;
-    pp.expected_rows = T * K > 64 ? T * K : 64;
-    pp.msg_stride = g.msg_stride, pp.recv_x = a->packed_recv_x;
-    pp.recv_scales = a->packed_recv_x_scales, pp.recv_src_info = a->packed_recv_src_info;
-    pp.recv_count = a->packed_recv_count, pp.layout_range = a->packed_recv_layout_range;
+    char* area = b->base + kHeaderRegion + (size_t)par * g.parity_bytes;
+    mcep::GroupDispatchParams p = {};
+    p.x = a->x, p.topk_idx = a->topk_idx, p.slot = sc.slot, p.count = sc.count;
+    p.peer_base = b->peer_dev, p.local_base = b->base;
+    p.T = T, p.K = K, p.E = E, p.R = R, p.M = M, p.H = H, p.rank = b->rank;
+    p.use_fp8 = fp8, p.fused = fused;
+    p.w = words_of(par, 0);
+    p.rx_off = (size_t)(area - b->base), p.meta_off = p.rx_off + g.meta_off;
+    p.row_bytes = g.row_bytes, p.meta_stride = g.meta_stride;
+    p.seq = seq;
+    p.wait.active_ranks = a->active_ranks, p.wait.timeout_ns = to_ns(a->timeout_us);
+    p.wait.hard_timeout_ns = b->hard_timeout_ns, p.wait.status = b->status;
+    p.res_cnt = sc.res_cnt, p.res_dflag = sc.res_dflag, p.ticket = sc.send_ticket;
+    p.rowmap = sc.rowmap;
+    p.recv_x = a->packed_recv_x, p.recv_scales = a->packed_recv_x_scales;
+    p.recv_src_info = a->packed_recv_src_info, p.recv_count = a->packed_recv_count;
+    p.layout_range = a->packed_recv_layout_range;
+    // the caller either took the tensor mcep_buffer_next_recv_x names (rows land in
+    // it, nothing to copy) or passes memory of its own (rows are copied out)
+    p.copy_rows = (a->packed_recv_x != static_cast<void*>(area));
+
+    auto& rec = b->record[par];
+    rec.key = a->packed_recv_src_info, rec.seq = seq;
+    rec.T = T, rec.K = K, rec.E = E, rec.M = M, rec.H = H;
 
     const bool pdl = b->pdl;
     const int num_sms = b->num_sms;
-    // Small batches in a group, no hook: both phases in one launch.
-    const bool one_kernel = fused && !direct && !a->return_recv_hook && b->one_kernel &&
-                            mcep::call_can_be_one_kernel(T, K, H, num_sms);
+    // Small batches, rows in place, no hook: one launch does it all.
+    bool one_kernel = fused && !p.copy_rows && !a->return_recv_hook && b->one_kernel &&
+                      mcep::group_call_can_be_one_kernel(T, K, E, num_sms);
+    if (b->defer) {
+        MCEP_REQUIRE(!a->async_finish);
+        b->pending.kind = 1, b->pending.phases = one_kernel ? 3 : 1, b->pending.d = p;
+        b->pending.then_second = !one_kernel && !a->return_recv_hook;
+        b->pending.stream = compute;
+        if (a->return_recv_hook) {
+            auto* h = new mcep_hook();
+            h->fn = [=]() {
+                mcep::LaunchCtx c0{compute, num_sms, false};
+                MCEP_CUDA(mcep::launch_group_dispatch_recv(p, c0));
+                return MCEP_OK;
+            };
+            *out_hook = h;
+        }
+        return MCEP_OK;
+    }
     if (one_kernel) {
-        cudaError_t e1 = mcep::launch_dispatch_one_kernel(sp, pp, first);
+        cudaError_t e1 = mcep::launch_group_dispatch(p, first);
         if (e1 == cudaErrorInvalidConfiguration) {
             cudaGetLastError();  // would not be resident at once on this device: two launches
-            MCEP_CUDA(mcep::launch_dispatch_send(sp, first));
-            MCEP_CUDA(mcep::launch_dispatch_recv(pp, next));
+            one_kernel = false;
         } else {
             MCEP_CUDA(e1);
         }
-    } else {
-        MCEP_CUDA(mcep::launch_dispatch_send(sp, fused ? first : next));
     }
+    if (!one_kernel) MCEP_CUDA(mcep::launch_group_dispatch_send(p, fused ? first : next));
     auto recv = [=](cudaStream_t s, bool chained) -> int {
-        if (direct || one_kernel) return MCEP_OK;
+        if (one_kernel) return MCEP_OK;
         mcep::LaunchCtx c0{s, num_sms, chained && pdl};
-        MCEP_CUDA(mcep::launch_dispatch_recv(pp, c0));
+        MCEP_CUDA(mcep::launch_group_dispatch_recv(p, c0));
         return MCEP_OK;
     };
 
@@ -482,15 +672,7 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
         return MCEP_OK;
     }
     if (int rc = recv(stream, true)) return rc;
-    if (a->async_finish) {
-        auto* ev = new mcep_event();
-        if (cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventRecord(ev->ev, stream) != cudaSuccess) {
-            delete ev;
-            return fail(MCEP_ERR_CUDA, "Failed: CUDA error creating the completion event");
-        }
-        *out_event = ev;
-    }
+    if (a->async_finish) return completion_event(stream, out_event);
     return MCEP_OK;
 }
 
@@ -511,93 +693,194 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
     MCEP_REQUIRE(T >= 0 && T <= M);
     MCEP_REQUIRE(K >= 1 && K <= MCEP_MAX_TOPK);
     MCEP_REQUIRE(!(a->async_finish && a->return_recv_hook));
-    MCEP_REQUIRE(T == 0 || (a->x != nullptr && a->topk_idx != nullptr && a->topk_weights != nullptr));
+    MCEP_REQUIRE(T == 0 || (a->topk_idx != nullptr && a->topk_weights != nullptr));
+    MCEP_REQUIRE(a->zero_copy || T == 0 || a->x != nullptr);
     MCEP_REQUIRE(a->src_info != nullptr && a->layout_range != nullptr);
     MCEP_REQUIRE(a->active_ranks != nullptr);
     MCEP_REQUIRE(T == 0 || a->combined_x != nullptr);
-    if (a->zero_copy)
-        return fail(MCEP_ERR_INVALID,
-                    "Failed: zero-copy combine is not supported; pass the expert output tensor "
-                    "with zero_copy=False");
     MCEP_REQUIRE(aligned(a->x, 32) && aligned(a->combined_x, 32));
     MCEP_REQUIRE((size_t)T * K <= b->scratch_entries);
     if (int rc = check_connected(b)) return rc;
 
-    const bool direct = (R == 1) && !b->force_staged;
+    const bool group = is_group(b);
     const Geometry g = geometry(R, E, M, H, false);
-    if (!direct && 2 * g.parity_bytes > (size_t)b->num_bytes)
+    if (group && 2 * g.parity_bytes > (size_t)b->num_bytes)
         return fail(MCEP_ERR_INVALID,
                     "Failed: Assertion error %s:%d 'layout.total_bytes <= num_ep_buffer_bytes' "
                     "(need %zu, have %lld)",
                     __FILE__, __LINE__, 2 * g.parity_bytes, (long long)b->num_bytes);
 
-    const uint32_t seq = ++b->seq;
-    const int par = seq & 1;
-    auto& sc = b->scratch[par];
-    const size_t cstage_off = kHeaderRegion + (size_t)par * g.parity_bytes + g.dstage_bytes;
-    const size_t cflag_off = (size_t)(par * 2 + 1) * kFlagBlock;
-
     cudaStream_t compute = reinterpret_cast<cudaStream_t>(a->compute_stream);
     cudaStream_t stream = a->async_finish ? b->comm_stream : compute;
-    if (a->async_finish)
-        if (int rc = order_after(stream, compute, b->ev_a)) return rc;
-    mcep::LaunchCtx first{stream, b->num_sms, false};
-
-    // small single-rank batches: the reduce kernel finds the rows in the handle itself
-    const bool search = direct && (long long)T * K <= 4096;
-    if (direct && !search) {
-        mcep::CombineInvertParams ip = {};
-        ip.src_info = a->src_info, ip.layout_range = a->layout_range, ip.topk_idx = a->topk_idx;
-        ip.L = g.L, ip.R = R, ip.M = M, ip.T = T, ip.K = K, ip.rank = b->rank;
-        ip.rowmap = sc.rowmap, ip.status = b->status;
-        MCEP_CUDA(mcep::launch_combine_invert(ip, first));
-    }
-    mcep::CombineSendParams sp = {};
-    sp.x = a->x, sp.src_info = a->src_info, sp.layout_range = a->layout_range;
-    sp.active_ranks = a->active_ranks, sp.peer_base = b->peer_dev, sp.done = sc.cdone;
-    sp.L = g.L, sp.R = R, sp.M = M, sp.H = H, sp.rank = b->rank;
-    sp.stage_off = cstage_off, sp.flag_off = cflag_off, sp.seq = seq, sp.status = b->status;
-    const bool one_kernel = !direct && !a->return_recv_hook && b->one_kernel &&
-                            mcep::call_can_be_one_kernel(T, K, H, b->num_sms);
-    if (!direct && !one_kernel) MCEP_CUDA(mcep::launch_combine_send(sp, first));
-
-    mcep::CombineReduceParams rp = {};
-    rp.topk_idx = a->topk_idx, rp.topk_weights = a->topk_weights, rp.active_ranks = a->active_ranks;
-    rp.T = T, rp.K = K, rp.E = E, rp.L = g.L, rp.M = M, rp.H = H;
-    rp.w.flags = reinterpret_cast<const uint64_t*>(b->base + cflag_off);
-    rp.w.resolved = sc.cres, rp.w.active_ranks = a->active_ranks, rp.w.seq = seq;
-    rp.w.timeout_ns = to_ns(a->timeout_us), rp.w.hard_timeout_ns = b->hard_timeout_ns;
-    rp.w.status = b->status;
-    rp.stage = b->base + cstage_off, rp.direct = direct, rp.x = a->x, rp.rowmap = sc.rowmap;
-    rp.RM = g.RM, rp.combined_x = a->combined_x;
-    rp.search = search, rp.src_info = a->src_info, rp.layout_range = a->layout_range;
-
     const bool pdl = b->pdl;
     const int num_sms = b->num_sms;
-    if (one_kernel) MCEP_CUDA(mcep::launch_combine_one_kernel(sp, rp, first));
-    auto recv = [=](cudaStream_t s, bool chained) -> int {
+
+    if (!group) {
+        // a single rank gathers straight from the expert-output tensor; with
+        // zero_copy the caller's tensor IS the combine buffer (nothing differs)
+        const uint32_t seq = ++b->cseq;
+        auto& sc = b->scratch[seq & 1];
+        if (a->async_finish)
+            if (int rc = order_after(stream, compute, b->ev_a)) return rc;
+        mcep::LaunchCtx first{stream, num_sms, false};
+        // small batches: the reduce kernel finds the rows in the handle itself
+        const bool search = (long long)T * K <= 4096;
+        if (!search) {
+            mcep::CombineInvertParams ip = {};
+            ip.src_info = a->src_info, ip.layout_range = a->layout_range, ip.topk_idx = a->topk_idx;
+            ip.L = E, ip.R = 1, ip.M = M, ip.T = T, ip.K = K, ip.rank = 0;
+            ip.rowmap = sc.rowmap, ip.status = b->status;
+            MCEP_CUDA(mcep::launch_combine_invert(ip, first));
+        }
+        mcep::DirectCombineParams dp = {};
+        dp.topk_idx = a->topk_idx, dp.topk_weights = a->topk_weights;
+        dp.active_ranks = a->active_ranks;
+        dp.T = T, dp.K = K, dp.E = E, dp.M = M, dp.H = H;
+        dp.x = a->x, dp.rowmap = sc.rowmap, dp.search = search;
+        dp.src_info = a->src_info, dp.layout_range = a->layout_range;
+        dp.combined_x = a->combined_x;
+        auto reduce = [=](cudaStream_t s, bool chained) -> int {
+            mcep::LaunchCtx c0{s, num_sms, chained && pdl && !search};
+            MCEP_CUDA(mcep::launch_direct_combine(dp, c0));
+            return MCEP_OK;
+        };
+        if (a->return_recv_hook) {
+            auto* h = new mcep_hook();
+            h->fn = [=]() { return reduce(compute, false); };
+            *out_hook = h;
+            return MCEP_OK;
+        }
+        if (int rc = reduce(stream, true)) return rc;
+        if (a->async_finish) return completion_event(stream, out_event);
+        return MCEP_OK;
+    }
+
+    // Which dispatch call does this handle come from? Its rows' positions at the
+    // experts' owners were recorded then; the two most recent calls are kept.
+    const mcep_buffer::DispatchRecord* rec = nullptr;
+    for (int i = 0; i < 2; ++i) {
+        const auto& c = b->record[i];
+        if (c.key != nullptr && c.key == a->src_info && (rec == nullptr || c.seq > rec->seq)) rec = &c;
+    }
+    if (rec == nullptr)
+        return fail(MCEP_ERR_STATE,
+                    "Failed: Assertion error %s:%d 'combine needs the handle of one of the last two "
+                    "dispatch calls of this buffer'",
+                    __FILE__, __LINE__);
+    if (rec->T != T || rec->K != K || rec->E != E || rec->M != M || rec->H != H)
+        return fail(MCEP_ERR_INVALID,
+                    "Failed: Assertion error %s:%d 'combine arguments match the dispatch call of the "
+                    "handle' (dispatch: T=%d K=%d E=%d M=%d H=%d)",
+                    __FILE__, __LINE__, rec->T, rec->K, rec->E, rec->M, rec->H);
+    const int dpar = rec->seq & 1;
+
+    const uint32_t seq = ++b->cseq;
+    const int par = seq & 1;
+    if (a->async_finish)
+        if (int rc = order_after(stream, compute, b->ev_a)) return rc;
+    mcep::LaunchCtx first{stream, num_sms, false};
+
+    mcep::GroupCombineParams p = {};
+    p.x = a->x, p.layout_range = a->layout_range, p.topk_idx = a->topk_idx;
+    p.topk_weights = a->topk_weights, p.rowmap = b->scratch[dpar].rowmap;
+    p.peer_base = b->peer_dev, p.local_base = b->base;
+    p.T = T, p.K = K, p.E = E, p.R = R, p.M = M, p.H = H, p.rank = b->rank;
+    p.zero_copy = a->zero_copy != 0;
+    p.w = words_of(0, par);
+    p.cin_off = kHeaderRegion + (size_t)par * g.parity_bytes + g.darea_bytes;
+    p.seq = seq;
+    p.wait.active_ranks = a->active_ranks, p.wait.timeout_ns = to_ns(a->timeout_us);
+    p.wait.hard_timeout_ns = b->hard_timeout_ns, p.wait.status = b->status;
+    p.res_cflag = b->scratch[par].res_cflag, p.ticket = b->scratch[par].publish_ticket;
+    p.combined_x = a->combined_x;
+
+    const bool one_kernel = !a->return_recv_hook && b->one_kernel &&
+                            mcep::group_call_can_be_one_kernel(T, K, E, num_sms);
+    if (b->defer && !a->return_recv_hook) {
+        // The publish phase waits for nobody and can be launched rank by rank,
+        // the reduce phase only once every rank has published; both phases in one
+        // launch need all ranks in that launch.
+        MCEP_REQUIRE(!a->async_finish);
+        if (!one_kernel) MCEP_CUDA(mcep::launch_group_combine_publish(p, first));
+        b->pending.kind = 2, b->pending.phases = one_kernel ? 3 : 2, b->pending.c = p;
+        b->pending.then_second = false, b->pending.stream = compute;
+        return MCEP_OK;
+    }
+    if (one_kernel)
+        MCEP_CUDA(mcep::launch_group_combine(p, first));
+    else
+        MCEP_CUDA(mcep::launch_group_combine_publish(p, first));
+    auto reduce = [=](cudaStream_t s, bool chained) -> int {
         if (one_kernel) return MCEP_OK;
-        mcep::LaunchCtx c0{s, num_sms, chained && pdl && !search};
-        MCEP_CUDA(mcep::launch_combine_reduce(rp, c0));
+        mcep::LaunchCtx c0{s, num_sms, chained && pdl};
+        MCEP_CUDA(mcep::launch_group_combine_reduce(p, c0));
         return MCEP_OK;
     };
 
     if (a->return_recv_hook) {
         auto* h = new mcep_hook();
-        h->fn = [=]() { return recv(compute, false); };
+        h->fn = [=]() { return reduce(compute, false); };
         *out_hook = h;
         return MCEP_OK;
     }
-    if (int rc = recv(stream, true)) return rc;
-    if (a->async_finish) {
-        auto* ev = new mcep_event();
-        if (cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming) != cudaSuccess ||
-            cudaEventRecord(ev->ev, stream) != cudaSuccess) {
-            delete ev;
-            return fail(MCEP_ERR_CUDA, "Failed: CUDA error creating the completion event");
-        }
-        *out_event = ev;
+    if (int rc = reduce(stream, true)) return rc;
+    if (a->async_finish) return completion_event(stream, out_event);
+    return MCEP_OK;
+}
+
+// -----------------------------------------------------------------------------
+// in-process groups: start what the ranks have prepared, in one launch
+// -----------------------------------------------------------------------------
+int mcep_launch_deferred(mcep_buffer* const* bufs, int n) {
+    MCEP_REQUIRE(bufs != nullptr && n >= 1 && n <= mcep::kMaxRanks);
+    std::vector<mcep::GroupDispatchParams> dps;
+    std::vector<mcep::GroupCombineParams> cps;
+    std::vector<mcep_buffer*> who;
+    int kind = 0, phases = 0;
+    cudaStream_t stream = nullptr;
+    for (int i = 0; i < n; ++i) {
+        mcep_buffer* b = bufs[i];
+        MCEP_REQUIRE(b != nullptr);
+        if (b->pending.kind == 0) continue;
+        if (kind == 0) kind = b->pending.kind, phases = b->pending.phases, stream = b->pending.stream;
+        MCEP_REQUIRE(b->pending.kind == kind && b->pending.phases == phases);
+        MCEP_REQUIRE(b->pending.stream == stream && b->device == bufs[0]->device);
+        if (kind == 1) dps.push_back(b->pending.d); else cps.push_back(b->pending.c);
+        who.push_back(b);
     }
+    if (kind == 0) return MCEP_OK;
+    mcep_buffer* b0 = who[0];
+    const size_t need = kind == 1 ? sizeof(mcep::GroupDispatchParams) * dps.size()
+                                  : sizeof(mcep::GroupCombineParams) * cps.size();
+    static void* dev_params = nullptr;
+    static size_t dev_params_bytes = 0;
+    if (need > dev_params_bytes) {
+        if (dev_params) cudaFree(dev_params);
+        dev_params = nullptr, dev_params_bytes = 0;
+        MCEP_CUDA(cudaMalloc(&dev_params, need));
+        dev_params_bytes = need;
+    }
+    mcep::LaunchCtx ctx{stream, b0->num_sms, false};
+    if (kind == 2 && phases == 2) {  // every rank has published: the reduce phases, rank by rank
+        for (mcep_buffer* b : who) {
+            b->pending.kind = 0;
+            MCEP_CUDA(mcep::launch_group_combine_reduce(b->pending.c, ctx));
+        }
+        return MCEP_OK;
+    }
+    cudaError_t e;
+    if (kind == 1)
+        e = mcep::launch_group_dispatch_multi(dps.data(), (int)dps.size(),
+                                              static_cast<mcep::GroupDispatchParams*>(dev_params),
+                                              phases, ctx);
+    else
+        e = mcep::launch_group_combine_multi(cps.data(), (int)cps.size(),
+                                             static_cast<mcep::GroupCombineParams*>(dev_params), ctx);
+    for (mcep_buffer* b : who) b->pending.kind = 0;
+    MCEP_CUDA(e);
+    if (kind == 1)
+        for (mcep_buffer* b : who)
+            if (b->pending.then_second) MCEP_CUDA(mcep::launch_group_dispatch_recv(b->pending.d, ctx));
     return MCEP_OK;
 }
 

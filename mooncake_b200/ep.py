@@ -48,9 +48,9 @@ class _CombineArgs(_c.Structure):
 
 
 def _load() -> ctypes.CDLL:
-    path = _build.LIB
-    if not os.path.exists(path):
-        path = _build.build()
+    # builds the library when it is missing or older than its sources (where the
+    # sources and a compiler are present; a prebuilt library alone is taken as is)
+    path = _build.build()
     L = ctypes.CDLL(path)
     vp, i32, i64, u64 = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_uint64
     sig = {
@@ -72,6 +72,12 @@ def _load() -> ctypes.CDLL:
         "mcep_buffer_set_peer_bases": (i32, [vp, _c.POINTER(vp), _c.POINTER(_c.c_int32)]),
         "mcep_buffer_set_option": (i32, [vp, _c.c_char_p, i64]),
         "mcep_buffer_status": (i32, [vp, _c.POINTER(_c.c_int32), i32]),
+        "mcep_buffer_call_counts": (i32, [vp, _c.POINTER(_c.c_uint32), _c.POINTER(_c.c_uint32)]),
+        "mcep_buffer_next_recv_x": (i32, [vp, i32, i32, i32, i32, _c.POINTER(vp),
+                                          _c.POINTER(_c.c_size_t)]),
+        "mcep_buffer_next_combine_buffer": (i32, [vp, i32, i32, i32, _c.POINTER(vp),
+                                                  _c.POINTER(_c.c_size_t)]),
+        "mcep_launch_deferred": (i32, [_c.POINTER(vp), i32]),
         "mcep_dispatch": (i32, [vp, _c.POINTER(_DispatchArgs), _c.POINTER(vp), _c.POINTER(vp)]),
         "mcep_combine": (i32, [vp, _c.POINTER(_CombineArgs), _c.POINTER(vp), _c.POINTER(vp)]),
         "mcep_event_create": (i32, [u64, _c.POINTER(vp)]),
@@ -85,6 +91,7 @@ def _load() -> ctypes.CDLL:
         "mcep_combine_single_rank_static": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp,
                                                   u64]),
         "mcep_static_last_error": (_c.c_char_p, []),
+        "mcep_static_status": (i32, [_c.POINTER(_c.c_int32)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -255,6 +262,30 @@ class Buffer:
         _check(_lib.mcep_buffer_status(self._h, out, 1))
         return int(out[0])
 
+    def call_counts(self) -> Tuple[int, int]:
+        """(dispatch calls, combine calls) made or adopted so far."""
+        d, c = _c.c_uint32(), _c.c_uint32()
+        _check(_lib.mcep_buffer_call_counts(self._h, _c.byref(d), _c.byref(c)))
+        return int(d.value), int(c.value)
+
+    def next_recv_x(self, num_max_dispatch_tokens_per_rank: int, hidden: int, num_experts: int,
+                    use_fp8: bool) -> Tuple[int, int]:
+        """(device pointer, bytes) of the in-place receive tensor of the next
+        dispatch call, (0, 0) when there is none (include/mcep.h)."""
+        p, n = _c.c_void_p(), _c.c_size_t()
+        _check(_lib.mcep_buffer_next_recv_x(self._h, num_max_dispatch_tokens_per_rank, hidden,
+                                            num_experts, int(use_fp8), _c.byref(p), _c.byref(n)))
+        return int(p.value or 0), int(n.value)
+
+    def next_combine_buffer(self, num_max_dispatch_tokens_per_rank: int, hidden: int,
+                            num_experts: int) -> Tuple[int, int]:
+        """(device pointer, bytes) of the tensor the next zero-copy combine reads."""
+        p, n = _c.c_void_p(), _c.c_size_t()
+        _check(_lib.mcep_buffer_next_combine_buffer(self._h, num_max_dispatch_tokens_per_rank,
+                                                    hidden, num_experts, _c.byref(p),
+                                                    _c.byref(n)))
+        return int(p.value or 0), int(n.value)
+
     # -- the hot path ----------------------------------------------------------
     def dispatch(self, x_ptr: int, topk_idx_ptr: int, active_ranks_ptr: int, num_tokens: int,
                  hidden: int, num_topk: int, num_max_dispatch_tokens_per_rank: int,
@@ -302,6 +333,13 @@ class Buffer:
                 _Hook(hk.value) if hk.value else None)
 
 
+def launch_deferred(buffers: List["Buffer"]) -> None:
+    """In-process groups: start, as one launch, the calls the given buffers have
+    prepared under option "defer_launch" (include/mcep.h: mcep_launch_deferred)."""
+    arr = (_c.c_void_p * len(buffers))(*[b._h for b in buffers])
+    _check(_lib.mcep_launch_deferred(arr, len(buffers)))
+
+
 def routing_layout(topk_idx_ptr: int, num_tokens: int, num_topk: int, num_experts: int,
                    num_ranks: int, count_ptr: int, rank_count_ptr: int, expert_prefix_ptr: int,
                    slot_ptr: int, scratch_ptr: int, stream_ptr: int = 0) -> None:
@@ -334,3 +372,12 @@ def combine_single_rank_static(x_ptr: int, topk_idx_ptr: int, topk_weights_ptr: 
                                               combined_x_ptr, stream_ptr)
     if rc != 0:
         raise RuntimeError(_lib.mcep_static_last_error().decode())
+
+
+def static_status() -> int:
+    """Anomaly bits the allocation-free combine's kernels recorded on the current
+    device since the last call of this function (0 = clean); reading clears them."""
+    out = _c.c_int32(0)
+    if _lib.mcep_static_status(_c.byref(out)) != 0:
+        raise RuntimeError(_lib.mcep_static_last_error().decode())
+    return int(out.value)

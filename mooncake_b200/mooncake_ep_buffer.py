@@ -9,6 +9,16 @@ and error behaviour. What is different underneath:
   active rank the constructor raises instead of degrading;
 * rows of an expert arrive in a fixed order (source rank, then token index),
   which is the order the reference's torch path produces;
+* in a group the returned `recv_x` is a view of the buffer's symmetric memory:
+  peers store the rows there directly, so dispatch moves no payload on the
+  receiving side. It stays valid until the dispatch call after the next one
+  on this buffer (two calls may be in flight, as with the reference's double
+  buffering); `Buffer(..., recv_in_place=False)` returns a fresh tensor instead,
+  at the price of one copy;
+* zero-copy combine is built: `get_next_combine_buffer(handle)` returns the
+  symmetric tensor the next `combine(..., zero_copy=True)` reads (the reference
+  documents it, docs/source/design/mooncake-ep.md:165-167, and rejects it,
+  :551,680);
 * the bootstrap only all-gathers the 64-byte memory handles
   (reference :271-285); the RDMA metadata exchange (:188-264) does not exist.
 """
@@ -22,12 +32,19 @@ import torch.distributed as dist
 
 from . import ep
 
-_ZERO_COPY_MSG = ("Mooncake EP zero-copy combine is not supported; pass the expert output "
-                  "tensor to combine() with zero_copy=False")
-
-
 def _stream_ptr() -> int:
     return int(torch.cuda.current_stream().cuda_stream)
+
+
+class _DeviceBytes:
+    """A span of the buffer's symmetric memory, exposed through the CUDA array
+    interface so torch can wrap it without copying. Holds the runtime object:
+    tensors made from it keep the allocation alive."""
+
+    def __init__(self, owner: object, ptr: int, nbytes: int):
+        self._owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (ptr, False), "version": 3}
 
 
 class EventOverlap:
@@ -53,7 +70,9 @@ class EventOverlap:
 
 class Buffer:
     def __init__(self, group: dist.ProcessGroup, num_ep_buffer_bytes: int = 0,
-                 disable_p2p: bool = False):
+                 disable_p2p: bool = False, recv_in_place: bool = True):
+        self.recv_in_place = recv_in_place
+        self._views = {}
         self.rank = group.rank()
         self.group_size = group.size()
         self.group = group
@@ -126,6 +145,17 @@ class Buffer:
             return torch.ones((self.group_size,), dtype=torch.int32, device=device)
         return active_ranks
 
+    def _symmetric_tensor(self, ptr: int, nbytes: int, shape: tuple, dtype: torch.dtype,
+                          device: torch.device) -> torch.Tensor:
+        """A tensor over `nbytes` of symmetric memory at `ptr` (made once per span)."""
+        views = self.__dict__.setdefault("_views", {})
+        key = (ptr, nbytes, shape, dtype)
+        t = views.get(key)
+        if t is None:
+            raw = torch.as_tensor(_DeviceBytes(self.runtime, ptr, nbytes), device=device)
+            t = views[key] = raw.view(dtype).view(shape)
+        return t
+
     # ----------------------------------------------------------------- dispatch
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, active_ranks: torch.Tensor,
                  num_max_dispatch_tokens_per_rank: int, num_experts: int, timeout_us: int,
@@ -154,8 +184,14 @@ class Buffer:
         R, M, H = self.group_size, num_max_dispatch_tokens_per_rank, x.size(1)
         L = num_experts // R
         dev = x.device
-        recv_x = torch.empty((L, R * M, H), device=dev,
-                             dtype=torch.float8_e4m3fn if use_fp8 else torch.bfloat16)
+        rx_dtype = torch.float8_e4m3fn if use_fp8 else torch.bfloat16
+        recv_x = None
+        if getattr(self, "recv_in_place", True):
+            ptr, nbytes = self.runtime.next_recv_x(M, H, num_experts, use_fp8)
+            if ptr:
+                recv_x = self._symmetric_tensor(ptr, nbytes, (L, R * M, H), rx_dtype, dev)
+        if recv_x is None:
+            recv_x = torch.empty((L, R * M, H), device=dev, dtype=rx_dtype)
         recv_count = torch.empty((L,), dtype=torch.int32, device=dev)
         src_info = torch.empty((L, R * M), dtype=torch.int32, device=dev)
         layout_range = torch.empty((L, R), dtype=torch.int64, device=dev)
@@ -182,9 +218,9 @@ class Buffer:
                 return_recv_hook: bool = False, out: Optional[torch.Tensor] = None
                 ) -> Tuple[torch.Tensor, EventOverlap, Optional[Callable]]:
         """Bring the expert outputs back and reduce them with the top-k weights
-        (reference :538-678)."""
-        if zero_copy:
-            raise NotImplementedError(_ZERO_COPY_MSG)
+        (reference :538-678). With `zero_copy` the expert outputs are read from the
+        tensor `get_next_combine_buffer(handle)` returned and `x` only gives the
+        shape."""
         assert x.dim() == 3 and x.is_contiguous()
         assert x.dtype == torch.bfloat16
         assert topk_idx.dim() == 2 and topk_idx.is_contiguous()
@@ -221,5 +257,15 @@ class Buffer:
         keep = (x, topk_idx, topk_weights, src_info, layout_range, combined_x)
         return combined_x, EventOverlap(event, keep if async_finish else None), hook
 
-    def get_next_combine_buffer(self, handle: object):
-        raise NotImplementedError(_ZERO_COPY_MSG)
+    def get_next_combine_buffer(self, handle: tuple) -> torch.Tensor:
+        """The tensor `[E/R, R*M, H]` bf16 the next `combine(..., zero_copy=True)`
+        reads: write the expert outputs into it instead of a tensor of your own.
+        A single rank has no symmetric memory to write into; it gets an ordinary
+        tensor and passes it to combine as `x`."""
+        src_info, _, M, hidden, num_experts = handle
+        R = self.group_size
+        shape = (num_experts // R, R * M, hidden)
+        ptr, nbytes = self.runtime.next_combine_buffer(M, hidden, num_experts)
+        if not ptr:
+            return torch.empty(shape, dtype=torch.bfloat16, device=src_info.device)
+        return self._symmetric_tensor(ptr, nbytes, shape, torch.bfloat16, src_info.device)

@@ -1,7 +1,10 @@
 """Shared helpers of the GPU tests: seeded inputs for the benchmark shapes and
-an in-process group that runs several logical ranks one after the other on one
-GPU (all sends first, then all receives, so no kernel ever waits for a later
-launch)."""
+an in-process group of several logical ranks on one GPU. In a group the ranks'
+kernels wait for one another (an expert's owner answers every source), so the
+logical ranks never run as separate launches: each prepares its call
+("defer_launch") and `ep.launch_deferred` starts all of them as ONE cooperative
+launch. Phases that wait for nothing launched later (a receive phase after
+every send phase has completed) run rank by rank."""
 from __future__ import annotations
 
 import math
@@ -56,29 +59,42 @@ class FakeGroup:
 
 
 def local_group(R: int, num_bytes: int, force_staged: bool = True,
-                hard_timeout_ms: int = 2000) -> List[Buffer]:
+                hard_timeout_ms: int = 2000, recv_in_place: bool = True) -> List[Buffer]:
     """R logical ranks on the current device, mapped to each other directly."""
     bufs = []
     for r in range(R):
         b = Buffer.__new__(Buffer)
         b.rank, b.group_size, b.group, b.backend = r, R, None, None
         b.num_ep_buffer_bytes = num_bytes
+        b.recv_in_place = recv_in_place
+        b._views = {}
         b.runtime = ep.Buffer(r, R, num_bytes, False)
         b._use_fallback = False
         b._warned_active_ranks = True
         b.runtime.set_option("hard_timeout_ms", hard_timeout_ms)
         if force_staged:
             b.runtime.set_option("force_staged", 1)
+        if R > 1 or force_staged:
+            b.runtime.set_option("defer_launch", 1)
         bufs.append(b)
-    bases = [b.runtime.local_base() for b in bufs]
-    for b in bufs:
-        b.runtime.set_peer_bases(bases)
+    connect_local_group(bufs)
     return bufs
 
 
-def run_dispatch(bufs, xs, idxs, M, E, use_fp8, active=None, timeout_us=200_000):
-    """SEND on every participating rank, then RECV on every one. Returns per rank
-    (recv_x, scales, recv_count, handle, active_ranks_tensor) or None."""
+def connect_local_group(bufs: List[Buffer], available: Optional[List[int]] = None) -> None:
+    """(Re)connect an in-process group: what `Buffer.connect` does with memory
+    handles and an all-gather, done with base pointers. Also brings the ranks'
+    call counters back in step (membership refresh)."""
+    bases = [b.runtime.local_base() for b in bufs]
+    for b in bufs:
+        b.runtime.set_peer_bases(bases, available)
+
+
+def run_dispatch(bufs, xs, idxs, M, E, use_fp8, active=None, timeout_us=200_000, mode="hook"):
+    """Dispatch on every participating rank. mode "hook": send phase of all ranks
+    (one launch), then every rank's receive phase from its hook; mode "sync": no
+    hook - small batches then run both phases in the one launch. Returns per rank
+    a dict (recv_x, scales, recv_count, handle, active) or None."""
     R = len(bufs)
     act = [1] * R if active is None else list(active)
     pend = [None] * R
@@ -86,23 +102,30 @@ def run_dispatch(bufs, xs, idxs, M, E, use_fp8, active=None, timeout_us=200_000)
         if not act[r]:
             continue
         ar = torch.tensor(act, dtype=torch.int32, device="cuda")
-        rx, cnt, handle, _, hook = bufs[r].dispatch(xs[r].cuda(), idxs[r].cuda(), ar, M, E,
-                                                     timeout_us, use_fp8=use_fp8,
-                                                     return_recv_hook=True)
-        pend[r] = (rx, cnt, handle, hook, ar)
+        dx, di = xs[r].cuda(), idxs[r].cuda()
+        rx, cnt, handle, _, hook = bufs[r].dispatch(dx, di, ar, M, E, timeout_us, use_fp8=use_fp8,
+                                                     return_recv_hook=(mode == "hook"))
+        pend[r] = (rx, cnt, handle, hook, ar, dx, di)
+    ep.launch_deferred([bufs[r].runtime for r in range(R) if pend[r] is not None])
     out = [None] * R
     for r in range(R):
         if pend[r] is None:
             continue
-        rx, cnt, handle, hook, ar = pend[r]
-        hook()
+        rx, cnt, handle, hook, ar = pend[r][:5]
+        if hook:
+            hook()
         out[r] = dict(recv_x=rx[0] if use_fp8 else rx, scales=rx[1] if use_fp8 else None,
                       recv_count=cnt, handle=handle, active=ar)
     torch.cuda.synchronize()
     return out
 
 
-def run_combine(bufs, ys, idxs, ws, handles, active=None, timeout_us=200_000):
+def run_combine(bufs, ys, idxs, ws, handles, active=None, timeout_us=200_000, mode="hook",
+                zero_copy=False):
+    """Combine on every participating rank. mode "hook": every rank's first phase
+    (it waits for nobody), then every rank's reduce from its hook; mode "sync":
+    both phases of all ranks in one launch. With zero_copy the expert outputs are
+    first written into `get_next_combine_buffer`."""
     R = len(bufs)
     act = [1] * R if active is None else list(active)
     pend = [None] * R
@@ -111,15 +134,21 @@ def run_combine(bufs, ys, idxs, ws, handles, active=None, timeout_us=200_000):
             continue
         ar = torch.tensor(act, dtype=torch.int32, device="cuda")
         di, dw = idxs[r].cuda(), ws[r].cuda()  # read again by the receive phase: keep alive
-        out, _, hook = bufs[r].combine(ys[r], di, dw, ar, timeout_us, handles[r],
-                                       return_recv_hook=True)
-        pend[r] = (out, hook, ar, di, dw)
+        y = ys[r]
+        if zero_copy:
+            bufs[r].get_next_combine_buffer(handles[r]).copy_(y)
+            y = torch.empty_like(y)  # only its shape is looked at
+        out, _, hook = bufs[r].combine(y, di, dw, ar, timeout_us, handles[r], zero_copy=zero_copy,
+                                       return_recv_hook=(mode == "hook"))
+        pend[r] = (out, hook, ar, di, dw, y)
+    ep.launch_deferred([bufs[r].runtime for r in range(R) if pend[r] is not None])
     res = [None] * R
     for r in range(R):
         if pend[r] is None:
             continue
         out, hook, ar = pend[r][:3]
-        hook()
+        if hook:
+            hook()
         res[r] = (out, ar)
     torch.cuda.synchronize()
     return res

@@ -3,7 +3,8 @@ the bootstrap). Started by tests/test_gpu_multi.py through torch.distributed.run
 
 Every rank regenerates all ranks' seeded inputs, runs dispatch + combine through
 the public `Buffer` API concurrently with its peers, and compares its own
-outputs with the CPU oracle. Exit code 0 = parity on this rank."""
+outputs with the CPU oracle (full-size cases: with properties that need no
+oracle). Exit code 0 = parity on this rank."""
 import json
 import os
 import sys
@@ -42,10 +43,13 @@ def run_case(cfg, group, rank, R, buf_cache):
         dist.barrier()
     if not active[rank]:
         return  # an inactive rank makes no call
+    buf.recv_in_place = cfg.get("recv_in_place", True)
     x, idx, w = xs[rank].cuda(), idxs[rank].cuda(), ws[rank].cuda()
     ar = torch.tensor(active, dtype=torch.int32, device="cuda")
+    if cfg.get("check") == "properties":
+        return run_full_size_case(cfg, buf, rank, R, xs, idxs, ws, x, idx, w, ar)
     want = ora.dispatch(xs, idxs, M, E, cfg["fp8"], active=active)[rank]
-    for rep in range(cfg.get("reps", 2)):  # twice: flags, counters and parities are reused
+    for rep in range(cfg.get("reps", 2)):  # twice: words, tickets and parities are reused
         mode = cfg.get("mode", "sync")
         recv, cnt, handle, ev, hook = buf.dispatch(
             x, idx, ar, M, E, cfg.get("timeout_us", 5_000_000), use_fp8=cfg["fp8"],
@@ -72,8 +76,12 @@ def run_case(cfg, group, rank, R, buf_cache):
         else:
             deq = recv
         y = mock_expert(torch.nan_to_num(deq.float()).to(torch.bfloat16), rank, L).contiguous()
+        zero_copy = cfg.get("zero_copy", False)
+        if zero_copy:
+            buf.get_next_combine_buffer(handle).copy_(y)
+            y = torch.empty_like(y)  # only its shape is looked at
         out, ev, hook = buf.combine(y, idx, w, ar, cfg.get("timeout_us", 5_000_000), handle,
-                                    async_finish=(mode == "async"),
+                                    zero_copy=zero_copy, async_finish=(mode == "async"),
                                     return_recv_hook=(mode == "hook"))
         if hook:
             hook()
@@ -96,6 +104,41 @@ def run_case(cfg, group, rank, R, buf_cache):
             err = float((out.cpu().float() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
             assert err < 2e-2, f"combine rel err {err}"
         assert buf.runtime.status() == 0, "device status word set"
+
+
+def run_full_size_case(cfg, buf, rank, R, xs, idxs, ws, x, idx, w, ar):
+    """Sizes the CPU oracle cannot finish in seconds, checked through properties:
+    per-expert counts equal a histogram of all ranks' indices, every segment of
+    sampled experts holds its source's rows in token order, and combine with an
+    identity expert gives x * sum(w) within bf16 rounding."""
+    M, E, H = cfg["M"], cfg["E"], cfg["H"]
+    L = E // R
+    recv, cnt, handle, _, _ = buf.dispatch(x, idx, ar, M, E, cfg.get("timeout_us", 5_000_000),
+                                           use_fp8=False)
+    torch.cuda.synchronize()
+    src_info, layout_range = handle[0], handle[1]
+    mine = torch.arange(rank * L, (rank + 1) * L)
+    per_src = torch.stack([torch.bincount(i.view(-1), minlength=E)[mine] for i in idxs], dim=1)
+    assert torch.equal(cnt.cpu(), per_src.sum(dim=1).to(torch.int32)), "recv_count"
+    lr = layout_range.cpu()
+    assert torch.equal(lr & 0xFFFFFFFF, per_src), "layout_range counts"
+    for le in (0, L // 2, L - 1):
+        for src in range(R):
+            begin, n = int(lr[le, src] >> 32), int(lr[le, src] & 0xFFFFFFFF)
+            toks = src_info[le, begin:begin + n].cpu().long()
+            assert bool((toks[1:] > toks[:-1]).all()), "token order"
+            assert bool((idxs[src][toks] == rank * L + le).any(dim=1).all()), "src_info"
+            assert torch.equal(recv[le, begin:begin + n].cpu(), xs[src][toks]), "payload"
+    for zero_copy in (False, True):
+        if zero_copy:
+            buf.get_next_combine_buffer(handle).copy_(recv)
+        out, _, _ = buf.combine(recv, idx, w, ar, cfg.get("timeout_us", 5_000_000), handle,
+                                zero_copy=zero_copy)
+        torch.cuda.synchronize()
+        ref = xs[rank].float() * ws[rank].sum(dim=1, keepdim=True)
+        err = float((out.cpu().float() - ref).abs().max() / ref.abs().max())
+        assert err < 1e-2, f"combine rel err {err} (zero_copy={zero_copy})"
+    assert buf.runtime.status() == 0, "device status word set"
 
 
 def main():

@@ -73,13 +73,23 @@ def test_no_device_is_a_loud_error_not_a_fallback():
         ep.Buffer(0, 1, 1 << 20)
 
 
-def test_zero_copy_is_rejected_like_the_reference():
+def test_zero_copy_surface_exists_and_shapes_the_combine_buffer():
+    """`get_next_combine_buffer(handle)` (documented by the reference,
+    docs/source/design/mooncake-ep.md:165-167, rejected by its wrapper,
+    mooncake_ep_buffer.py:680-681) returns `[E/R, R*M, H]` bf16; where the runtime
+    names no symmetric tensor (a single rank) it is an ordinary tensor."""
+    import torch
     from mooncake_b200.mooncake_ep_buffer import Buffer
+
+    class _NoSymmetricMemory:
+        def next_combine_buffer(self, M, hidden, num_experts):
+            return 0, 0
+
     b = Buffer.__new__(Buffer)
-    with pytest.raises(NotImplementedError, match="zero-copy combine is not supported"):
-        b.get_next_combine_buffer(None)
-    with pytest.raises(NotImplementedError):
-        b.combine(None, None, None, None, 0, (), zero_copy=True)
+    b.group_size, b.runtime = 2, _NoSymmetricMemory()
+    src_info = torch.zeros((4, 2 * 8), dtype=torch.int32)
+    t = b.get_next_combine_buffer((src_info, None, 8, 128, 8))
+    assert t.shape == (4, 16, 128) and t.dtype == torch.bfloat16
 
 
 _C_KINDS = {"int32_t": ("i", 4), "int64_t": ("i", 8), "uint64_t": ("u", 8)}

@@ -26,11 +26,28 @@ def _cases(R):
         "mixtral_t1024": dict(T=1024, M=1024, H=4096, E=8, K=2, fp8=False),
         "ragged": dict(tokens=[(7 * r) % 50 for r in range(R)], M=64, H=640, E=8 * R, K=3,
                        fp8=True, mask=6),
+        # zero-copy combine, and a caller-owned recv_x (rows copied out, as the
+        # reference's wrapper would ask for)
+        "decode_fp8_zero_copy": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, seed=5,
+                                     zero_copy=True),
+        "decode_fp8_zero_copy_hook": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, seed=6,
+                                          zero_copy=True, mode="hook"),
+        "decode_fp8_caller_recv_x": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, seed=7,
+                                         recv_in_place=False),
+        # config 5's largest point, and config 3 at its full 4096 tokens per rank
+        # (checked through properties, the oracle does not finish these in seconds)
+        "mixtral_t4096": dict(T=4096, M=4096, H=4096, E=8, K=2, fp8=False, check="properties"),
+        "prefill_t4096": dict(T=4096, M=4096, H=7168, E=256, K=8, fp8=False, check="properties"),
     }
     if R >= 2:
-        # the last rank is marked inactive on every rank and makes no call
-        c["masked_last_rank"] = dict(T=64, M=64, H=4096, E=8, K=2, fp8=False,
+        # the last rank is marked inactive on every rank and makes no call for three
+        # layers; after a membership refresh it is back in step
+        c["masked_last_rank"] = dict(T=64, M=64, H=4096, E=8, K=2, fp8=False, reps=3,
                                      active=[1] * (R - 1) + [0])
+        c["rejoined_after_refresh"] = dict(T=64, M=64, H=4096, E=8, K=2, fp8=False, seed=8,
+                                           refresh_members=True)
+        c["rejoined_decode_fp8"] = dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, seed=9,
+                                        refresh_members=True)
     return c
 
 
@@ -44,7 +61,7 @@ def test_multi_gpu_parity(R):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={R}",
            "--master-addr", "127.0.0.1", "--master-port", str(29620 + R),
            os.path.join(ROOT, "tests", "mp_worker.py")]
-    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     out = p.stdout + p.stderr
     log_dir = os.environ.get("MCEP_TEST_LOG_DIR", "")
     if os.path.isdir(log_dir):  # keep the whole log of the child processes

@@ -225,9 +225,10 @@ def test_time_reference_kernels_beside_ours_single_gpu():
     res = {}
     for mode, staged in (("direct", 0), ("staged", 1)):
         buf.runtime.set_option("force_staged", staged)
+        t_d = _bench(lambda: buf.dispatch(dx, di, ar, M, E, 200_000, use_fp8=True))
+        # (combine takes the handle of one of the buffer's last two dispatch calls)
         _, _, handle, _, _ = buf.dispatch(dx, di, ar, M, E, 200_000, use_fp8=True)
-        res[mode] = (_bench(lambda: buf.dispatch(dx, di, ar, M, E, 200_000, use_fp8=True)),
-                     _bench(lambda: buf.combine(y, di, dw, ar, 200_000, handle)))
+        res[mode] = (t_d, _bench(lambda: buf.combine(y, di, dw, ar, 200_000, handle)))
     out = dict(shape="128 tok, hidden 7168, 256 experts, top-8, fp8 dispatch, 1 GPU",
                reference_kernel_us=dict(dispatch=t_ref_d, combine=t_ref_c, layer=t_ref_d + t_ref_c),
                ours_direct_us=dict(dispatch=res["direct"][0], combine=res["direct"][1],

@@ -7,8 +7,8 @@ expert: the received count against the gathered routing (:63-64), every row
 against its `src_info` and the `layout_range` segment of its source rank
 (:66-75), the combine result against the closed form `x * sum(valid weights)`
 (:92-94, difference below 1e-5), and that repeating a call gives the same
-bytes (:77-80). Here the ranks of a group run one after the other on one GPU
-(all sends first, then all receives).
+bytes (:77-80). Here the ranks of a group are logical ranks on one GPU: their
+send phases run as one launch, then every rank's receive phase.
 """
 from __future__ import annotations
 
@@ -20,7 +20,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from ep_harness import FakeGroup, local_group  # noqa: E402
-from mooncake_b200 import Buffer  # noqa: E402
+from mooncake_b200 import Buffer, ep  # noqa: E402
 
 RANK_OFFSET = 128  # codes rank - 128 .. stay exact in bf16 and in e4m3 * scale
 
@@ -67,6 +67,7 @@ def _layer(bufs, xs, idxs, ws, T, E, use_fp8):
     for r in range(R):
         pend.append(bufs[r].dispatch(xs[r], idxs[r], active, T, E, -1, use_fp8=use_fp8,
                                      return_recv_hook=True))
+    ep.launch_deferred([b.runtime for b in bufs])  # logical ranks: all send phases in one launch
     for p in pend:
         p[4]()
     torch.cuda.synchronize()

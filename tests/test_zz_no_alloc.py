@@ -40,6 +40,26 @@ def test_static_combine_matches_regular_combine_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"call {call}"
         assert buf.runtime.status() == 0
+        assert ep.static_status() == 0  # the entry point's own anomaly word (read and cleared)
+
+
+def test_static_combine_reports_a_bad_handle_instead_of_partial_sums_in_silence():
+    """A handle whose token indices are out of range cannot be combined; the
+    kernels skip those rows and say so in the word `mcep_static_status` reads."""
+    T, H, E, K = 16, 256, 4, 2
+    buf = Buffer(FakeGroup(0, 1), 0)
+    active = torch.ones(1, dtype=torch.int32, device="cuda")
+    x, idx, w = _case(23, T, H, E, K, n_mask=0)
+    recv, cnt, handle, _, _ = buf.dispatch(x, idx, active, T, E, 200_000, use_fp8=False)
+    bad_src_info = handle[0].clone()
+    le = int((cnt > 0).nonzero()[0])  # an expert that received something
+    bad_src_info[le, 0] = T + 5  # a token index the caller never had
+    out = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    ep.combine_single_rank_static(recv.data_ptr(), idx.data_ptr(), w.data_ptr(),
+                                  bad_src_info.data_ptr(), handle[1].data_ptr(), E, T, H, K, T,
+                                  out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert ep.static_status() == 4
+    assert ep.static_status() == 0  # reading cleared it
 
 
 def test_static_combine_rejects_sizes_beyond_its_scratch():
