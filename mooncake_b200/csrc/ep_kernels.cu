@@ -422,6 +422,125 @@ __global__ void __launch_bounds__(1024)
     }
 }
 
+// ---- the same layout in two passes over token chunks ------------------------------
+// The kernel above lets every block read the whole index matrix (each block owns
+// some experts). For large batches that costs more than the work itself, so the
+// usual route is two small kernels in which a block owns a CHUNK of tokens and
+// reads only that chunk:
+//   pass 1  per-chunk histogram of the (de-duplicated) expert choices;
+//   pass 2  per expert, the count of all earlier chunks (a short column sum) plus
+//           the position inside the chunk (bitmap + popcount, as above) = slot;
+//           the block of the last chunk also writes the totals.
+// A repeated expert inside a token counts once; token order is the only order.
+// One lane per token: the token's K choices are requested together (one memory
+// round trip) and de-duplicated in registers; e[k] = -1 for masked, out-of-range
+// and repeated entries.
+__device__ __forceinline__ void load_token_choices(const int64_t* topk_idx, int t, int T, int K, int E,
+                                                   int (&e)[kMaxTopk]) {
+#pragma unroll
+    for (int k = 0; k < kMaxTopk; ++k) {
+        e[k] = -1;
+        if (t < T && k < K) {
+            const int v = (int)__ldg(topk_idx + (size_t)t * K + k);
+            e[k] = (v >= 0 && v < E) ? v : -1;
+        }
+    }
+#pragma unroll
+    for (int k = 1; k < kMaxTopk; ++k) {
+        bool dup = false;
+#pragma unroll
+        for (int kk = 0; kk < k; ++kk) dup |= (e[kk] == e[k]);
+        if (dup) e[k] = -1;
+    }
+}
+
+// a chunk is `warps` x 32 tokens: warp w of the block takes tokens [32w, 32w + 32)
+__global__ void __launch_bounds__(256) ep_layout_hist_kernel(LayoutParams p) {
+    extern __shared__ int smem_i32[];
+    int* hist = smem_i32;  // [E]
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int t = blockIdx.x * nthr + tid;
+    int e[kMaxTopk];
+    load_token_choices(p.topk_idx, t, p.T, p.K, p.E, e);
+    for (int i = tid; i < p.E; i += nthr) hist[i] = 0;
+    __syncthreads();
+    pdl_wait();
+    pdl_launch_dependents();
+#pragma unroll
+    for (int k = 0; k < kMaxTopk; ++k)
+        if (e[k] >= 0) atomicAdd(&hist[e[k]], 1);
+    __syncthreads();
+    for (int i = tid; i < p.E; i += nthr) p.chunk_hist[(size_t)blockIdx.x * p.E + i] = hist[i];
+}
+
+__global__ void __launch_bounds__(256) ep_layout_slot_kernel(LayoutParams p) {
+    extern __shared__ int smem_i32[];
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, words = nthr >> 5;
+    int* base = smem_i32;                                          // [E] tokens of earlier chunks
+    uint32_t* mask = reinterpret_cast<uint32_t*>(smem_i32 + p.E);  // [E][words], word w written by warp w only
+    const int t = blockIdx.x * nthr + tid;
+    int e[kMaxTopk];
+    load_token_choices(p.topk_idx, t, p.T, p.K, p.E, e);
+    for (int i = tid; i < p.E * words; i += nthr) mask[i] = 0;
+    __syncthreads();
+    // bit (expert, token): lanes of a warp that chose the same expert in the same
+    // position k form a group; its lowest lane ORs the group into the warp's word
+    for (int k = 0; k < p.K; ++k) {
+        const unsigned key = e[k] >= 0 ? (unsigned)e[k] : (0x80000000u | lane);
+        const unsigned grp = __match_any_sync(kFull, key);
+        if (e[k] >= 0 && (int)(__ffs(grp) - 1) == lane) mask[e[k] * words + warp] |= grp;
+        __syncwarp();
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int i = tid; i < p.E; i += nthr) {
+        int sum = 0;
+        for (int c = 0; c < (int)blockIdx.x; ++c) sum += __ldcg(p.chunk_hist + (size_t)c * p.E + i);
+        base[i] = sum;
+    }
+    __syncthreads();
+    if (t < p.T) {
+        const unsigned lower = (1u << lane) - 1u;
+#pragma unroll
+        for (int k = 0; k < kMaxTopk; ++k) {
+            if (k >= p.K) break;
+            int slot = -1;
+            if (e[k] >= 0) {
+                const uint32_t* m = mask + e[k] * words;
+                slot = base[e[k]] + __popc(m[warp] & lower);
+                for (int w = 0; w < warp; ++w) slot += __popc(m[w]);
+            }
+            p.slot[(size_t)t * p.K + k] = slot;
+        }
+    }
+    if (blockIdx.x != gridDim.x - 1) return;
+    // the block of the last chunk knows every total
+    __syncthreads();
+    for (int i = tid; i < p.E; i += nthr) {
+        int c = base[i];
+        for (int w = 0; w < words; ++w) c += __popc(mask[i * words + w]);
+        base[i] = c;
+        p.count[i] = c;
+        if (p.recv_count) p.recv_count[i] = c;
+        if (p.layout_range) p.layout_range[i] = c;  // begin 0 | count
+    }
+    if (p.rank_count == nullptr && p.expert_prefix == nullptr) return;
+    __syncthreads();
+    const int L = p.E / p.R;
+    for (int r = warp; r < p.R; r += words) {
+        int carry = 0;
+        for (int b = 0; b < L; b += 32) {
+            const int le = b + lane;
+            const int c = le < L ? base[r * L + le] : 0;
+            const int incl = warp_inclusive_scan(c, lane);
+            if (le < L && p.expert_prefix) p.expert_prefix[r * L + le] = carry + incl - c;
+            carry += __shfl_sync(kFull, incl, 31);
+        }
+        if (lane == 0 && p.rank_count) p.rank_count[r] = carry;
+    }
+}
+
 // =============================================================================
 // sending token rows (single rank and groups)
 // =============================================================================
@@ -616,7 +735,7 @@ __device__ __forceinline__ void send_tokens(const SendView& v, int first_token, 
                     }
                 }
             }
-            if (kGroup && tid < v.K) v.rowmap[(size_t)t * v.K + tid] = row;
+            if (tid < v.K && v.rowmap != nullptr) v.rowmap[(size_t)t * v.K + tid] = row;
             if (scan_now && e >= 0) kmap[e] = -1;  // leave the table clean for the next token
             s_dst[tid] = dst;
             s_meta[tid] = meta;
@@ -698,6 +817,7 @@ __global__ void __launch_bounds__(512) ep_dispatch_send_direct_kernel(DirectDisp
     v.L = p.E, v.RM = p.M, v.status = p.status;
     v.recv_x = reinterpret_cast<char*>(p.recv_x), v.recv_scales = p.recv_scales;
     v.recv_src_info = p.recv_src_info, v.row_bytes = p.H * (kFP8 ? 1 : 2);
+    v.rowmap = p.rowmap;
     send_tokens<kFP8, false, kFused>(v, blockIdx.x, gridDim.x, hist, kmap);
     if (kFused) {
         // the receive layout of a single rank, spread over the grid. A block
@@ -1411,7 +1531,32 @@ using namespace kernels;
 // =============================================================================
 // launchers
 // =============================================================================
+// The chunked route: chunks of up to 256 tokens (fewer when the per-chunk bitmap
+// of all experts would not fit 48 KB of shared memory), at most 128 chunks, and
+// per-chunk histograms that fit the scratch the caller gave.
+static bool layout_chunking(const LayoutParams& p, int* chunk_tokens, int* words, int* chunks) {
+    if (p.chunk_hist == nullptr || p.T < 512) return false;
+    int w = (int)(12288 / p.E) - 1;  // (1 + w) * E ints of shared memory, 48 KB at most
+    if (w > 8) w = 8;
+    if (w < 1) return false;
+    const int ct = w * 32;
+    const int c = (p.T + ct - 1) / ct;
+    if (c > 128 || (size_t)c * p.E > p.chunk_hist_entries) return false;
+    *chunk_tokens = ct, *words = w, *chunks = c;
+    return true;
+}
+
 cudaError_t launch_layout(const LayoutParams& p, const LaunchCtx& ctx) {
+    int chunk_tokens = 0, cwords = 0, chunks = 0;
+    if (layout_chunking(p, &chunk_tokens, &cwords, &chunks)) {
+        cudaError_t e = launch("ep_layout_hist", ep_layout_hist_kernel, dim3(chunks),
+                               dim3(chunk_tokens), (size_t)p.E * sizeof(int), ctx, p);
+        if (e != cudaSuccess) return e;
+        LaunchCtx chained = ctx;
+        chained.pdl = true;
+        return launch("ep_layout_slot", ep_layout_slot_kernel, dim3(chunks), dim3(chunk_tokens),
+                      (size_t)p.E * (1 + cwords) * sizeof(int), chained, p);
+    }
     const int words = (p.T + 31) / 32 > 0 ? (p.T + 31) / 32 : 1;
     const long long n = (long long)p.T * p.K;
     // Every block reads the whole index matrix, so the number of blocks trades

@@ -40,6 +40,9 @@ struct LayoutParams {
     // single-rank groups: the layout already is the receive layout
     int32_t* recv_count;      // [E] or null
     int64_t* layout_range;    // [E] or null
+    // optional scratch for the two-pass (chunked) variant: per-chunk histograms
+    int32_t* chunk_hist;      // [chunk_hist_entries] or null
+    size_t chunk_hist_entries;
 };
 cudaError_t launch_layout(const LayoutParams& p, const LaunchCtx& ctx);
 
@@ -58,6 +61,7 @@ struct DirectDispatchParams {
     int32_t* recv_src_info;
     int32_t* recv_count;        // fused: [E]
     int64_t* layout_range;      // fused: [E]
+    int32_t* rowmap;            // [T*K] row of (token, k) inside its expert, kept for combine
 };
 // whether a send kernel may count the slots itself for this problem size
 bool can_fuse_layout(int T, int K, int E, int num_sms);

@@ -48,6 +48,7 @@ int fail(int code, const char* fmt, ...) {
     } while (0)
 
 constexpr size_t kWorkspaceBytes = 32u << 20;  // as NUM_WORKSPACE_BYTES in the reference
+constexpr size_t kChunkHistBytes = 2u << 20;   // per-chunk histograms of the routing layout (per parity)
 // Front of the symmetric allocation, ahead of the caller-sized data area: the
 // words ranks write into each other's memory, twice (one set per parity):
 //   cnt   [MCEP_MAX_EXPERTS] u64   counts announced to this rank (owner side)
@@ -96,7 +97,7 @@ struct mcep_buffer {
 
     // workspace carve-up (per parity so two calls in flight do not share scratch)
     struct Scratch {
-        int32_t *slot, *count, *rowmap;
+        int32_t *slot, *count, *rowmap, *rowmap_inv, *chunk_hist;
         uint64_t *res_cnt, *res_dflag, *res_cflag;  // verdict words
         unsigned *layout_ticket, *send_ticket, *publish_ticket;
     } scratch[2];
@@ -248,8 +249,8 @@ int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int
     const size_t words = (size_t)MCEP_MAX_EXPERTS * sizeof(uint64_t);
     const size_t small = (size_t)(MCEP_MAX_EXPERTS + 64) * sizeof(int32_t);
     const size_t half = (kWorkspaceBytes - 256) / 2;
-    const size_t fixed = 256 + small + words + 2 * 64 * sizeof(uint64_t);
-    const size_t big = (half - fixed - 512) / 2;  // bytes for each of slot / rowmap
+    const size_t fixed = 256 + small + words + 2 * 64 * sizeof(uint64_t) + kChunkHistBytes;
+    const size_t big = ((half - fixed - 1024) / 3) / 256 * 256;  // bytes for each of slot / rowmap / rowmap_inv
     b->scratch_entries = big / sizeof(int32_t);
     for (int par = 0; par < 2; ++par) {
         char* w = b->workspace + 256 + par * half;
@@ -262,8 +263,10 @@ int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int
         s.res_cnt = reinterpret_cast<uint64_t*>(w), w += words;
         s.res_dflag = reinterpret_cast<uint64_t*>(w), w += 64 * sizeof(uint64_t);
         s.res_cflag = reinterpret_cast<uint64_t*>(w), w += 64 * sizeof(uint64_t);
-        s.slot = reinterpret_cast<int32_t*>(w), w += big / 256 * 256;
-        s.rowmap = reinterpret_cast<int32_t*>(w);
+        s.chunk_hist = reinterpret_cast<int32_t*>(w), w += kChunkHistBytes;
+        s.slot = reinterpret_cast<int32_t*>(w), w += big;
+        s.rowmap = reinterpret_cast<int32_t*>(w), w += big;
+        s.rowmap_inv = reinterpret_cast<int32_t*>(w);
     }
     if (const char* env = std::getenv("MCEP_DISABLE_PDL"))
         if (env[0] == '1') b->pdl = false;
@@ -576,6 +579,7 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
         lp.topk_idx = a->topk_idx;
         lp.T = T, lp.K = K, lp.E = E, lp.R = R;
         lp.count = sc.count, lp.slot = sc.slot, lp.ticket = sc.layout_ticket;
+        lp.chunk_hist = sc.chunk_hist, lp.chunk_hist_entries = kChunkHistBytes / sizeof(int32_t);
         if (!group) {
             lp.recv_count = a->packed_recv_count;
             lp.layout_range = a->packed_recv_layout_range;
@@ -591,6 +595,10 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
         dp.status = b->status, dp.recv_x = a->packed_recv_x;
         dp.recv_scales = a->packed_recv_x_scales, dp.recv_src_info = a->packed_recv_src_info;
         dp.recv_count = a->packed_recv_count, dp.layout_range = a->packed_recv_layout_range;
+        dp.rowmap = sc.rowmap;
+        auto& rec = b->record[par];
+        rec.key = a->packed_recv_src_info, rec.seq = seq;
+        rec.T = T, rec.K = K, rec.E = E, rec.M = M, rec.H = H;
         MCEP_CUDA(mcep::launch_direct_dispatch(dp, fused ? first : next));
         if (a->return_recv_hook) {
             auto* h = new mcep_hook();
@@ -723,24 +731,40 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
         if (a->async_finish)
             if (int rc = order_after(stream, compute, b->ev_a)) return rc;
         mcep::LaunchCtx first{stream, num_sms, false};
-        // small batches: the reduce kernel finds the rows in the handle itself
-        const bool search = (long long)T * K <= 4096;
-        if (!search) {
+        // The rows of (token, k) inside their experts: kept from the dispatch call
+        // when the handle is that of one of the last two; otherwise found again
+        // in the handle itself - by the reduce kernel (small batches) or by an
+        // inversion pass of its own.
+        const int32_t* rowmap = nullptr;
+        {
+            const mcep_buffer::DispatchRecord* rec = nullptr;
+            for (int i = 0; i < 2; ++i) {
+                const auto& c = b->record[i];
+                if (c.key != nullptr && c.key == a->src_info && (rec == nullptr || c.seq > rec->seq))
+                    rec = &c;
+            }
+            if (rec && rec->T == T && rec->K == K && rec->E == E && rec->M == M && rec->H == H)
+                rowmap = b->scratch[rec->seq & 1].rowmap;
+        }
+        const bool search = rowmap == nullptr && (long long)T * K <= 4096;
+        if (rowmap == nullptr && !search) {
             mcep::CombineInvertParams ip = {};
             ip.src_info = a->src_info, ip.layout_range = a->layout_range, ip.topk_idx = a->topk_idx;
             ip.L = E, ip.R = 1, ip.M = M, ip.T = T, ip.K = K, ip.rank = 0;
-            ip.rowmap = sc.rowmap, ip.status = b->status;
+            ip.rowmap = sc.rowmap_inv, ip.status = b->status;
             MCEP_CUDA(mcep::launch_combine_invert(ip, first));
+            rowmap = sc.rowmap_inv;
         }
+        const bool chain = rowmap == sc.rowmap_inv && !search;
         mcep::DirectCombineParams dp = {};
         dp.topk_idx = a->topk_idx, dp.topk_weights = a->topk_weights;
         dp.active_ranks = a->active_ranks;
         dp.T = T, dp.K = K, dp.E = E, dp.M = M, dp.H = H;
-        dp.x = a->x, dp.rowmap = sc.rowmap, dp.search = search;
+        dp.x = a->x, dp.rowmap = rowmap, dp.search = search;
         dp.src_info = a->src_info, dp.layout_range = a->layout_range;
         dp.combined_x = a->combined_x;
         auto reduce = [=](cudaStream_t s, bool chained) -> int {
-            mcep::LaunchCtx c0{s, num_sms, chained && pdl && !search};
+            mcep::LaunchCtx c0{s, num_sms, chained && pdl && chain};
             MCEP_CUDA(mcep::launch_direct_combine(dp, c0));
             return MCEP_OK;
         };
@@ -934,7 +958,7 @@ int mcep_hook_free(mcep_hook* h) {
 // -----------------------------------------------------------------------------
 // routing layout, standalone
 // -----------------------------------------------------------------------------
-size_t mcep_routing_layout_scratch_bytes(void) { return 256; }
+size_t mcep_routing_layout_scratch_bytes(void) { return 256 + kChunkHistBytes; }
 
 int mcep_routing_layout(const int64_t* topk_idx, int T, int K, int E, int R, int32_t* count,
                         int32_t* rank_count, int32_t* expert_prefix, int32_t* slot, void* scratch,
@@ -949,6 +973,8 @@ int mcep_routing_layout(const int64_t* topk_idx, int T, int K, int E, int R, int
     lp.topk_idx = topk_idx, lp.T = T, lp.K = K, lp.E = E, lp.R = R;
     lp.count = count, lp.slot = slot, lp.rank_count = rank_count, lp.expert_prefix = expert_prefix;
     lp.ticket = reinterpret_cast<unsigned*>(scratch);
+    lp.chunk_hist = reinterpret_cast<int32_t*>(static_cast<char*>(scratch) + 256);
+    lp.chunk_hist_entries = kChunkHistBytes / sizeof(int32_t);
     mcep::LaunchCtx ctx{reinterpret_cast<cudaStream_t>(stream), sms, false};
     MCEP_CUDA(mcep::launch_layout(lp, ctx));
     return MCEP_OK;

@@ -86,14 +86,26 @@ enum { MLX5_INLINE_SEG = 0x80000000 };
 """
 
 
-DEFAULT_MOONCAKE_SRC = os.environ.get("MOONCAKE_SRC", os.path.join(os.sep, "root", "reference"))
+def find_mooncake_src() -> str | None:
+    """Where the Mooncake sources lie: the environment variable MOONCAKE_SRC, or a
+    checkout named `reference` beside this repository. None when there is none."""
+    marker = os.path.join("mooncake-ep", "src", "mooncake_ep_kernel.cu")
+    cands = [os.environ.get("MOONCAKE_SRC"),
+             os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, marker)):
+            return c
+    return None
 
 
-def build_reference_kernels(reference_root: str = DEFAULT_MOONCAKE_SRC,
+def build_reference_kernels(reference_root: str | None = None,
                             force: bool = False) -> str | None:
     """Compile the reference kernel TU + harness. Returns the .so path, or
     None when no Mooncake checkout is present (then a prebuilt .so, if any,
     is used as is)."""
+    reference_root = reference_root or find_mooncake_src()
+    if reference_root is None:
+        return REF_SO if os.path.exists(REF_SO) else None
     ref_cu = os.path.join(reference_root, "mooncake-ep", "src",
                           "mooncake_ep_kernel.cu")
     harness = os.path.join(HERE, "ref_harness.cu")

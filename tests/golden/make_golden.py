@@ -26,7 +26,6 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-_DEFAULT_SRC = os.path.join(os.sep, "root", "reference")
 
 # name -> config. `tokens` is per rank (uneven on purpose in some cases).
 CASES = {
@@ -151,7 +150,9 @@ def _worker(rank: int, name: str, cfg: dict, reference_root: str, port: int, out
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("MOONCAKE_SRC", _DEFAULT_SRC))
+    ap.add_argument("--reference", default=os.environ.get("MOONCAKE_SRC"),
+                    required="MOONCAKE_SRC" not in os.environ,
+                    help="root of the Mooncake source tree (or set MOONCAKE_SRC)")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     torch.set_num_threads(2)

@@ -411,6 +411,33 @@ def test_masked_rank_rejoins_after_membership_refresh():
     _run_case(cfg, bufs=bufs, mode="sync")
 
 
+def test_idle_rank_keeps_in_step_over_several_layers():
+    """One rank has no tokens at all, another routes everything to its own
+    experts: neither exchanges payload with some of its peers. Every dispatch
+    call still exchanges counts and answers with every rank, so nobody can run
+    ahead of a slower peer by more than one call; several layers in a row, in
+    both launch modes, end without a timeout and with the oracle's results."""
+    R, M, H, E, K = 4, 32, 512, 16, 2
+    cfg = dict(R=R, tokens=[0, 32, 24, 32], M=M, H=H, E=E, K=K, fp8=True, seed=13)
+    bufs = local_group(R, Buffer.get_ep_buffer_size_hint(M, H, R, E))
+    xs, idxs, ws = _inputs(cfg)
+    idxs[1] = (idxs[1] % (E // R)) + 1 * (E // R)  # rank 1 keeps its tokens at home
+    for layer in range(6):
+        mode = "hook" if layer % 3 else "sync"
+        got = run_dispatch(bufs, xs, idxs, M, E, True, timeout_us=2_000_000, mode=mode)
+        _check_dispatch(cfg, got, ora.dispatch(xs, idxs, M, E, True), None)
+        ys = _expert_outputs(cfg, got, None)
+        handles = [g["handle"] for g in got]
+        res = run_combine(bufs, ys, idxs, ws, handles, timeout_us=2_000_000, mode=mode)
+        hd = [dict(src_info=h[0].cpu(), layout_range=h[1].cpu()) for h in handles]
+        want = ora.combine([y.cpu() for y in ys], idxs, ws, hd, M, E)
+        for r in range(R):
+            assert torch.equal(res[r][0].cpu().view(torch.int16), want[r].view(torch.int16))
+            assert got[r]["active"].tolist() == [1] * R and res[r][1].tolist() == [1] * R
+    for b in bufs:
+        assert b.runtime.status() == 0
+
+
 def test_rank_marked_active_without_a_mapping_is_left_alone():
     """active_ranks says 1 for a rank whose buffer was never mapped (masked out
     when the group connected): the kernels must not touch it. They treat it as
@@ -431,7 +458,10 @@ def test_rank_marked_active_without_a_mapping_is_left_alone():
 
 
 @pytest.mark.parametrize("T,K,E,R", [(128, 8, 256, 8), (4096, 8, 256, 1), (256, 8, 128, 8),
-                                     (1, 2, 8, 8), (0, 4, 16, 2), (777, 11, 288, 4)])
+                                     (1, 2, 8, 8), (0, 4, 16, 2), (777, 11, 288, 4),
+                                     # batches of 512 tokens and more take the two-pass route
+                                     (512, 16, 4096, 2), (5000, 3, 2048, 8), (4096, 2, 8, 8),
+                                     (40000, 2, 64, 2)])
 def test_routing_layout_kernel(T, K, E, R):
     g = torch.Generator().manual_seed(T + K)
     idx = torch.topk(torch.randn((max(T, 1), E), generator=g), K, dim=-1)[1][:T].contiguous()
