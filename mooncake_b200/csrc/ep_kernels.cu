@@ -435,8 +435,8 @@ __global__ void __launch_bounds__(1024)
 // One lane per token: the token's K choices are requested together (one memory
 // round trip) and de-duplicated in registers; e[k] = -1 for masked, out-of-range
 // and repeated entries.
-__device__ __forceinline__ void load_token_choices(const int64_t* topk_idx, int t, int T, int K, int E,
-                                                   int (&e)[kMaxTopk]) {
+__device__ __forceinline__ void request_token_choices(const int64_t* topk_idx, int t, int T, int K,
+                                                      int E, int (&e)[kMaxTopk]) {
 #pragma unroll
     for (int k = 0; k < kMaxTopk; ++k) {
         e[k] = -1;
@@ -445,6 +445,8 @@ __device__ __forceinline__ void load_token_choices(const int64_t* topk_idx, int 
             e[k] = (v >= 0 && v < E) ? v : -1;
         }
     }
+}
+__device__ __forceinline__ void drop_repeated_choices(int (&e)[kMaxTopk]) {
 #pragma unroll
     for (int k = 1; k < kMaxTopk; ++k) {
         bool dup = false;
@@ -452,6 +454,11 @@ __device__ __forceinline__ void load_token_choices(const int64_t* topk_idx, int 
         for (int kk = 0; kk < k; ++kk) dup |= (e[kk] == e[k]);
         if (dup) e[k] = -1;
     }
+}
+__device__ __forceinline__ void load_token_choices(const int64_t* topk_idx, int t, int T, int K, int E,
+                                                   int (&e)[kMaxTopk]) {
+    request_token_choices(topk_idx, t, T, K, E, e);
+    drop_repeated_choices(e);
 }
 
 // a chunk is `warps` x 32 tokens: warp w of the block takes tokens [32w, 32w + 32)
@@ -495,8 +502,16 @@ __global__ void __launch_bounds__(256) ep_layout_slot_kernel(LayoutParams p) {
     pdl_wait();
     pdl_launch_dependents();
     for (int i = tid; i < p.E; i += nthr) {
+        // column sum over the earlier chunks, eight loads in flight at a time
         int sum = 0;
-        for (int c = 0; c < (int)blockIdx.x; ++c) sum += __ldcg(p.chunk_hist + (size_t)c * p.E + i);
+        for (int c0 = 0; c0 < (int)blockIdx.x; c0 += 8) {
+            int v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                v[u] = c0 + u < (int)blockIdx.x ? __ldcg(p.chunk_hist + (size_t)(c0 + u) * p.E + i) : 0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) sum += v[u];
+        }
         base[i] = sum;
     }
     __syncthreads();
@@ -744,6 +759,13 @@ __device__ __forceinline__ void send_tokens(const SendView& v, int first_token, 
         }
         __syncthreads();
         if (kGroup) MCEP_TRACE(0, 7);  // the owners' answers are in, rows can go
+        // A repeated expert in a token's list was sent once; combine still adds
+        // that row once per listing (mooncake_ep_kernel.cu:734-742 reads the
+        // (expert, token) slot for every k), so the repeat records the same row.
+        if (tid < v.K && v.rowmap != nullptr && s_exp[tid] < 0 && s_raw[tid] >= 0) {
+            for (int kk = 0; kk < tid; ++kk)
+                if (s_exp[kk] == s_raw[tid]) v.rowmap[(size_t)t * v.K + tid] = s_row[kk];
+        }
 
         for (int tile = warp; tile < ntiles; tile += nwarps) {
             const int c = tile * 32 + lane;
@@ -997,37 +1019,45 @@ __device__ __forceinline__ void load_peer_tables(void* const* peer_base, const i
 //     source with the first row of its segment in each of this rank's experts.
 template <bool kFused>
 __device__ __forceinline__ void dispatch_control(const GroupDispatchParams& p, int* smem_i32,
-                                                 char* const* s_peer, const int* s_active) {
+                                                 char* const* s_peer, const int* s_active,
+                                                 int (&e)[kMaxTopk]) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int L = p.E / p.R, n = L * p.R;
     int* hist = smem_i32;                       // [E] (fused)
     int* s_cnt = smem_i32 + (kFused ? p.E : 0);  // [L*R]
-    int* s_beg = s_cnt + n;                      // [L*R]
     MCEP_TRACE(0, 1);
     if (kFused) {
-        int e_ahead[kScanAhead];
-        scan_prefetch(p.topk_idx, p.T, p.K, true, e_ahead);
-        for (int e = tid; e < p.E; e += nthr) hist[e] = 0;
+        // one lane per token: its choices arrive in one memory round trip
+        // (small batches: T <= 2 x the number of SMs, so one pass)
+        // (the caller requested this thread's token before the peer tables)
+        for (int i = tid; i < p.E; i += nthr) hist[i] = 0;
         __syncthreads();
-        scan_index_matrix<true, true>(p.topk_idx, p.T, p.K, p.E, hist, nullptr, nullptr, -1,
-                                      e_ahead);
+#pragma unroll
+        for (int k = 0; k < kMaxTopk; ++k)
+            if (e[k] >= 0) atomicAdd(&hist[e[k]], 1);
+        for (int t = tid + nthr; t < p.T; t += nthr) {
+            load_token_choices(p.topk_idx, t, p.T, p.K, p.E, e);
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k)
+                if (e[k] >= 0) atomicAdd(&hist[e[k]], 1);
+        }
         __syncthreads();
     }
-    for (int e = tid; e < p.E; e += nthr) {
-        const int dr = e / L;
+    for (int x = tid; x < p.E; x += nthr) {
+        const int dr = x / L;
         if (!s_active[dr]) continue;
-        const int c = kFused ? hist[e] : __ldg(p.count + e);
-        uint64_t* wd = reinterpret_cast<uint64_t*>(s_peer[dr] + p.w.cnt_off) + (p.rank * L + (e - dr * L));
+        const int c = kFused ? hist[x] : __ldg(p.count + x);
+        uint64_t* wd = reinterpret_cast<uint64_t*>(s_peer[dr] + p.w.cnt_off) + (p.rank * L + (x - dr * L));
         st_relaxed_sys(wd, ((uint64_t)p.seq << 32) | (uint32_t)(c + 1));
     }
     MCEP_TRACE(0, 2);  // counts announced
     const uint64_t* my_cnt = reinterpret_cast<const uint64_t*>(p.local_base + p.w.cnt_off);
     for (int i = tid; i < n; i += nthr) {
         const int le = i / p.R, src = i - le * p.R;
-        int c = 0;
+        int c = -1;  // -1: nothing will come from this source (inactive, or given up on)
         if (s_active[src]) {
             const uint32_t v = wait_word(my_cnt + src * L + le, p.seq, p.wait, src);
-            c = v ? (int)v - 1 : 0;
+            c = v ? (int)v - 1 : -1;
             if (c > p.M) {
                 atomicOr(p.wait.status, kStatusSlotRange);
                 c = 0;
@@ -1037,27 +1067,23 @@ __device__ __forceinline__ void dispatch_control(const GroupDispatchParams& p, i
     }
     __syncthreads();
     MCEP_TRACE(0, 3);  // every source's counts are in
-    for (int le = tid; le < L; le += nthr) {
-        int run = 0;
-        for (int src = 0; src < p.R; ++src) {
-            const int c = s_cnt[le * p.R + src];
-            s_beg[le * p.R + src] = run;
-            p.layout_range[le * p.R + src] = c ? (((int64_t)run << 32) | (int64_t)c) : 0;
-            run += c;
-        }
-        p.recv_count[le] = run;
-    }
-    __syncthreads();
+    // Every thread fixes its own (expert, source) entry: the rows of the lower
+    // sources come first. The answer goes out at once; the outputs follow.
     for (int i = tid; i < n; i += nthr) {
         const int le = i / p.R, src = i - le * p.R;
-        // a source that went silent while its counts were awaited sent count 0
-        // and gets no answer
-        if (s_active[src] && ld_volatile_s32(p.wait.active_ranks + src)) {
+        int begin = 0;
+        for (int s2 = 0; s2 < src; ++s2) begin += max(s_cnt[le * p.R + s2], 0);
+        // a source that is inactive, or went silent while its counts were
+        // awaited, counts as zero and gets no answer
+        const bool answered = s_cnt[i] >= 0;
+        const int c = max(s_cnt[i], 0);
+        if (answered) {
             uint64_t* wd = reinterpret_cast<uint64_t*>(s_peer[src] + p.w.beg_off) + (p.rank * L + le);
-            st_relaxed_sys(wd, ((uint64_t)p.seq << 32) | (uint32_t)(s_beg[i] + 1));
+            st_relaxed_sys(wd, ((uint64_t)p.seq << 32) | (uint32_t)(begin + 1));
         }
-        *reinterpret_cast<volatile uint64_t*>(p.res_cnt + i) =
-            ((uint64_t)p.seq << 32) | (uint32_t)(s_cnt[i] + 1);
+        *reinterpret_cast<volatile uint64_t*>(p.res_cnt + i) = ((uint64_t)p.seq << 32) | (uint32_t)(c + 1);
+        p.layout_range[i] = c ? (((int64_t)begin << 32) | (int64_t)c) : 0;
+        if (src == p.R - 1) p.recv_count[le] = begin + c;
     }
     MCEP_TRACE(0, 4);  // answers are out
 }
@@ -1211,11 +1237,16 @@ __device__ __forceinline__ void dispatch_body(const GroupDispatchParams& p, int 
     const int nsend = nblocks - 1;
     const int nh = nsend < kRecvHelpers ? nsend : kRecvHelpers;
     MCEP_TRACE(0, 0);
+    // the control block counts with one lane per token: its token's choices are
+    // requested first, so they travel while the peer tables are read
+    int ctl_choices[kMaxTopk];
+    if (kFused && bid == 0) request_token_choices(p.topk_idx, tid, p.T, p.K, p.E, ctl_choices);
     load_peer_tables(p.peer_base, p.wait.active_ranks, p.R, p.wait.status, s_peer, s_active);
+    if (kFused && bid == 0) drop_repeated_choices(ctl_choices);
 
     if (bid == 0) {
         __syncthreads();
-        dispatch_control<kFused>(p, smem_i32, s_peer, s_active);
+        dispatch_control<kFused>(p, smem_i32, s_peer, s_active, ctl_choices);
         if (kPhases == 3) {
             __syncthreads();
             dispatch_recv_duty<kFP8>(p, nh, nh + 1, smem_i32);

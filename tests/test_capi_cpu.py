@@ -92,6 +92,26 @@ def test_zero_copy_surface_exists_and_shapes_the_combine_buffer():
     assert t.shape == (4, 16, 128) and t.dtype == torch.bfloat16
 
 
+def test_pybind_binding_compiles_and_has_the_reference_module_surface(tmp_path):
+    """The compiled alternative to the ctypes binding (what would replace
+    mooncake-ep/src/ep_py.cpp): builds against include/mcep.h, links libmcep.so,
+    and exposes the names the reference's wrapper uses
+    (mooncake-wheel/mooncake/mooncake_ep_buffer.py:108-110, 185-304, 488-507, 641-660)."""
+    from tests.pybind_build import build_and_import
+    m = build_and_import(str(tmp_path))
+    assert m.MAX_QP_COUNT == 256
+    assert m.get_ep_buffer_size_hint(128, 7168, 8, 256) == 1883246592
+    for name in ("ibgda_disabled", "p2p_enabled", "use_fast_path", "is_roce", "update_local_qpns",
+                 "sync_ibgda_peers", "get_mr_info", "get_gid", "get_local_qpns", "get_local_lids",
+                 "get_ipc_handle", "sync_nvlink_ipc_handles", "dispatch", "combine"):
+        assert hasattr(m.Buffer, name), name
+    assert hasattr(m.EventHandle, "current_stream_wait") and hasattr(m.EventHandle, "synchronize")
+    import torch
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="Failed: CUDA error"):  # loud, no fallback
+            m.Buffer(0, 1, 1 << 20)
+
+
 _C_KINDS = {"int32_t": ("i", 4), "int64_t": ("i", 8), "uint64_t": ("u", 8)}
 
 

@@ -29,6 +29,10 @@ def _inputs(cfg):
                                      cfg["K"], cfg.get("routing", "uniform"), cfg.get("mask", 0))
         if cfg.get("mask_all"):
             idx.fill_(-1)
+        if cfg.get("repeats"):
+            # the same expert twice in a token's list (no valid router does this):
+            # sent once, added once per listing in combine
+            idx[::3, -1] = idx[::3, 0]
         xs.append(x), idxs.append(idx), ws.append(w)
     return xs, idxs, ws
 
@@ -135,6 +139,8 @@ CASES = {
     "ragged_bf16": dict(R=4, tokens=[7, 0, 64, 1], M=64, H=1152, E=12, K=3, fp8=False, mask=9),
     # one expert per rank, one choice per token
     "k1_l1": dict(R=4, T=32, M=32, H=256, E=4, K=1, fp8=True),
+    # a repeated expert inside a token's list
+    "repeats_fp8": dict(R=4, T=40, M=40, H=512, E=16, K=4, fp8=True, repeats=True, mask=5),
     # most choices a token may have
     "k16": dict(R=2, T=24, M=24, H=512, E=32, K=16, fp8=True, mask=20),
     # nothing to send at all: no tokens anywhere, and tokens whose every choice is masked
@@ -160,7 +166,7 @@ def test_group_matches_oracle(name):
 
 # small batches without a hook: both phases of a call in ONE launch (the path a
 # real group takes for decode-sized batches)
-ONE_LAUNCH = ["c1_bf16", "c1_fp8", "c2_fp8", "c4_fp8_zipf", "c5_r2_t1", "c5_r4_t16", "c5_r8_t128",
+ONE_LAUNCH = ["repeats_fp8", "c1_bf16", "c1_fp8", "c2_fp8", "c4_fp8_zipf", "c5_r2_t1", "c5_r4_t16", "c5_r8_t128",
               "ragged_fp8", "ragged_bf16", "k1_l1", "k16", "all_empty", "all_masked", "m_above_t",
               "r8_mixtral_t1", "r8_ragged"]
 
@@ -220,6 +226,8 @@ SINGLE = {
     "mixtral_fp8": dict(R=1, T=64, M=64, H=4096, E=8, K=2, fp8=True, mask=5),
     "empty": dict(R=1, T=0, M=8, H=256, E=4, K=2, fp8=True),
     "partial_tile": dict(R=1, T=33, M=40, H=896, E=6, K=3, fp8=True, mask=4),
+    "repeats": dict(R=1, T=48, M=48, H=512, E=8, K=4, fp8=False, repeats=True, mask=3),
+    "repeats_large": dict(R=1, T=1500, M=1500, H=256, E=32, K=5, fp8=True, repeats=True),
 }
 
 
@@ -248,10 +256,11 @@ def test_single_rank_group_path_plain_launches(name, mode):
     x, idx, w = xs[0].cuda(), idxs[0].cuda(), ws[0].cuda()
     want = ora.dispatch(xs, idxs, M, E, cfg["fp8"])
     kw = dict(async_finish=(mode == "async"))
+    small = T * K <= 4096 and T < 140  # decode-sized: one block per token, one launch per call
     for rep in range(3):  # both parities, and one reuse
         launches = ep.kernel_launch_count()
         rx, cnt, handle, ev, _ = buf.dispatch(x, idx, ar, M, E, 200_000, use_fp8=cfg["fp8"], **kw)
-        assert ep.kernel_launch_count() - launches == 1
+        assert not small or ep.kernel_launch_count() - launches == 1
         if mode == "async":
             ev.current_stream_wait()
         got = [dict(recv_x=rx[0] if cfg["fp8"] else rx, scales=rx[1] if cfg["fp8"] else None,
@@ -261,7 +270,7 @@ def test_single_rank_group_path_plain_launches(name, mode):
         ys = _expert_outputs(cfg, got, None)
         launches = ep.kernel_launch_count()
         out, ev, _ = buf.combine(ys[0], idx, w, ar, 200_000, handle, **kw)
-        assert ep.kernel_launch_count() - launches == 1
+        assert not small or ep.kernel_launch_count() - launches == 1
         if mode == "async":
             ev.current_stream_wait()
         torch.cuda.synchronize()

@@ -192,6 +192,9 @@ def _bench(fn, warm=10, iters=30):
     ts = []
     for _ in range(iters):
         flush.zero_()
+        # idle time on the device while the host runs ahead: the Python of the timed
+        # call is queued before the GPU reaches the first event
+        torch.cuda._sleep(400_000)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
@@ -202,45 +205,73 @@ def _bench(fn, warm=10, iters=30):
     return ts[len(ts) // 2]
 
 
-def test_time_reference_kernels_beside_ours_single_gpu():
-    """Decode shape on one GPU (128 tokens, hidden 7168, 256 experts, top-8, FP8
-    dispatch): median microseconds of dispatch and of combine, reference kernels
-    vs this repository's, same inputs, L2 flushed before every call."""
+TIMED_SHAPES = {
+    # BASELINE configurations as one rank sees them (all experts local)
+    "c1": dict(T=128, H=2048, E=16, K=4, fp8=False, routing="softmax"),
+    "c2": dict(T=128, H=7168, E=256, K=8, fp8=True),
+    "c3": dict(T=4096, H=7168, E=256, K=8, fp8=False),
+    "c4": dict(T=256, H=4096, E=128, K=8, fp8=True, routing="zipf1.2"),
+    "c5_t128": dict(T=128, H=4096, E=8, K=2, fp8=False),
+    "c5_t4096": dict(T=4096, H=4096, E=8, K=2, fp8=False),
+}
+
+
+@pytest.mark.parametrize("name", sorted(TIMED_SHAPES))
+def test_time_reference_kernels_beside_ours_single_gpu(name):
+    """Every BASELINE shape on one GPU: median microseconds of dispatch and of
+    combine, the reference's kernels (compiled for sm_100a) vs this repository's,
+    same inputs, L2 flushed before every call."""
     lib = _ref()
-    T = M = 128
-    H, E, K = 7168, 256, 8
-    x, idx, w = make_rank_inputs(33, 0, T, H, E, K)
+    cfg = TIMED_SHAPES[name]
+    T = M = cfg["T"]
+    H, E, K, fp8 = cfg["H"], cfg["E"], cfg["K"], cfg["fp8"]
+    big = T * K * H > (1 << 27)
+    warm, iters = (3, 10) if big else (10, 30)
+    x, idx, w = make_rank_inputs(33, 0, T, H, E, K, cfg.get("routing", "uniform"))
     dx, di, dw = x.cuda(), idx.cuda(), w.cuda()
-    rg = RefGroup(lib, 1, M, H, E)
-    ref = rg.dispatch([dx], [di], True, False)
     y = torch.randn((E, M, H), device="cuda").to(torch.bfloat16)
+    rg = RefGroup(lib, 1, M, H, E)
+    ref = rg.dispatch([dx], [di], fp8, False)
     # the reference side reuses preallocated outputs and never synchronises
     # inside the timed call: only its two launchers are between the events
     res_buf = [torch.empty((T, H), dtype=torch.bfloat16, device="cuda")]
-    t_ref_d = _bench(lambda: rg.dispatch([dx], [di], True, False, outs=ref, sync=False))
-    t_ref_c = _bench(lambda: rg.combine([y], [di], [dw], ref, False, res=res_buf, sync=False))
+    t_ref_d = _bench(lambda: rg.dispatch([dx], [di], fp8, False, outs=ref, sync=False), warm, iters)
+    t_ref_c = _bench(lambda: rg.combine([y], [di], [dw], ref, False, res=res_buf, sync=False), warm, iters)
+    del rg, ref
+    torch.cuda.empty_cache()
 
-    buf = Buffer(FakeGroup(0, 1), Buffer.get_ep_buffer_size_hint(M, H, 1, E))
-    ar = torch.ones(1, dtype=torch.int32, device="cuda")
     res = {}
-    for mode, staged in (("direct", 0), ("staged", 1)):
+    modes = (("direct", 0),) if big else (("direct", 0), ("group_path", 1))
+    for mode, staged in modes:
+        buf = Buffer(FakeGroup(0, 1), Buffer.get_ep_buffer_size_hint(M, H, 1, E) if staged else 0)
         buf.runtime.set_option("force_staged", staged)
-        t_d = _bench(lambda: buf.dispatch(dx, di, ar, M, E, 200_000, use_fp8=True))
+        ar = torch.ones(1, dtype=torch.int32, device="cuda")
+        t_d = _bench(lambda: buf.dispatch(dx, di, ar, M, E, 200_000, use_fp8=fp8), warm, iters)
         # (combine takes the handle of one of the buffer's last two dispatch calls)
-        _, _, handle, _, _ = buf.dispatch(dx, di, ar, M, E, 200_000, use_fp8=True)
-        res[mode] = (t_d, _bench(lambda: buf.combine(y, di, dw, ar, 200_000, handle)))
-    out = dict(shape="128 tok, hidden 7168, 256 experts, top-8, fp8 dispatch, 1 GPU",
+        _, _, handle, _, _ = buf.dispatch(dx, di, ar, M, E, 200_000, use_fp8=fp8)
+        res[mode] = (t_d, _bench(lambda: buf.combine(y, di, dw, ar, 200_000, handle), warm, iters))
+        del buf, handle
+        torch.cuda.empty_cache()
+    out = dict(shape=f"{name}: {T} tok, hidden {H}, {E} experts, top-{K}, "
+                     f"{'fp8' if fp8 else 'bf16'} dispatch, 1 GPU",
                reference_kernel_us=dict(dispatch=t_ref_d, combine=t_ref_c, layer=t_ref_d + t_ref_c),
-               ours_direct_us=dict(dispatch=res["direct"][0], combine=res["direct"][1],
-                                   layer=sum(res["direct"])),
-               ours_staged_us=dict(dispatch=res["staged"][0], combine=res["staged"][1],
-                                   layer=sum(res["staged"])),
-               note="median of 30, L2 flushed before each call, CUDA events around the call; "
+               ours_us={m: dict(dispatch=v[0], combine=v[1], layer=v[0] + v[1]) for m, v in res.items()},
+               note=f"median of {iters}, L2 flushed before each call, CUDA events around the call; "
                     "reference side = its two launchers with preallocated outputs, "
                     "our side = the full Buffer.dispatch/combine call")
     print("REFERENCE_KERNEL_TIMING " + json.dumps(out))
     d = os.environ.get("MCEP_TEST_LOG_DIR", "")
     if os.path.isdir(d):
-        with open(os.path.join(d, "ref_kernel_timing.json"), "w") as f:
-            json.dump(out, f, indent=1)
+        path = os.path.join(d, "ref_kernel_timing.json")
+        allres = {}
+        if os.path.exists(path):
+            try:
+                allres = json.load(open(path))
+                if "shape" in allres:  # a file of the single-shape format
+                    allres = {}
+            except Exception:
+                allres = {}
+        allres[name] = out
+        with open(path, "w") as f:
+            json.dump(allres, f, indent=1)
     assert t_ref_d > 0 and t_ref_c > 0

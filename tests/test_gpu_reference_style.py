@@ -145,3 +145,47 @@ def test_self_describing_payloads_single_rank(use_fp8):
     buf = Buffer(FakeGroup(0, 1), Buffer.get_ep_buffer_size_hint(T, H, 1, E))
     _check_layer(1, T, H, E, K, use_fp8, [buf], seed=2)
     assert buf.runtime.status() == 0
+
+
+def test_pybind_binding_drives_a_layer(tmp_path):
+    """The compiled pybind11 binding (mooncake_b200/csrc/ep_py_mcep.cpp) in the
+    place of `mooncake._ep`: one dispatch + combine on a single rank through its
+    `Buffer.dispatch` / `Buffer.combine`, with the pointer-and-int argument lists
+    of mooncake-ep/include/mooncake_ep_buffer.h:116-133, gives the bytes the
+    ctypes binding gives."""
+    from pybind_build import build_and_import
+    m = build_and_import(str(tmp_path))
+    T, H, E, K = 64, 2048, 16, 4
+    x, idx, w = _inputs(0, T, H, E, K, seed=3)
+    stream = torch.cuda.current_stream().cuda_stream
+    active = torch.ones(1, dtype=torch.int32, device="cuda")
+    ref_buf = Buffer(FakeGroup(0, 1), 0)
+    want_rx, want_cnt, want_handle, _, _ = ref_buf.dispatch(x, idx, active, T, E, 200_000, use_fp8=False)
+    want_out, _, _ = ref_buf.combine(want_rx, idx, w, active, 200_000, want_handle)
+
+    b = m.Buffer(0, 1, 0)
+    assert b.ibgda_disabled() and b.use_fast_path()
+    rx = torch.empty((E, T, H), dtype=torch.bfloat16, device="cuda")
+    cnt = torch.empty((E,), dtype=torch.int32, device="cuda")
+    src_info = torch.empty((E, T), dtype=torch.int32, device="cuda")
+    layout_range = torch.empty((E, 1), dtype=torch.int64, device="cuda")
+    ev, hook = b.dispatch(x.data_ptr(), idx.data_ptr(), active.data_ptr(), T, H, K, T, E, 200_000, False,
+                          rx.data_ptr(), 0, cnt.data_ptr(), src_info.data_ptr(), layout_range.data_ptr(),
+                          False, False, stream)
+    assert ev is None and hook is None
+    out = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    ev, hook = b.combine(rx.data_ptr(), idx.data_ptr(), w.data_ptr(), src_info.data_ptr(),
+                         layout_range.data_ptr(), active.data_ptr(), E, T, H, K, T, E, 200_000, False,
+                         out.data_ptr(), True, False, stream)
+    assert ev is not None and hook is None
+    ev.current_stream_wait(stream)
+    torch.cuda.synchronize()
+    assert torch.equal(cnt, want_cnt) and torch.equal(layout_range, want_handle[1])
+    for e in range(E):
+        n = int(cnt[e])
+        assert torch.equal(rx[e, :n], want_rx[e, :n]) and torch.equal(src_info[e, :n], want_handle[0][e, :n])
+    assert torch.equal(out.view(torch.int16), want_out.view(torch.int16))
+    with pytest.raises(RuntimeError, match="Failed: Assertion error"):
+        b.dispatch(x.data_ptr(), idx.data_ptr(), active.data_ptr(), T, H, K, T, E, 200_000, False,
+                   rx.data_ptr(), 0, cnt.data_ptr(), src_info.data_ptr(), layout_range.data_ptr(),
+                   True, True, stream)
