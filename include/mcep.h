@@ -40,6 +40,14 @@ extern "C" {
  * int32, as in mooncake-transfer-engine/src/transport/device/
  * p2p_device_transport.cpp:483-488. */
 #define MCEP_IPC_HANDLE_INT32S 16
+/* With MC_USE_NVLINK_IPC=0 in the environment, and where every visible device
+ * supports fabric handles, the buffer is a cuMemCreate allocation and the
+ * exported handle is a CUmemFabricHandle followed by the allocation's size:
+ * 72 bytes carried as 18 int32 (mooncake-transfer-engine/src/transport/device/
+ * p2p_device_transport.cpp:40-75, 271-386). Elsewhere the request is ignored
+ * and cudaMalloc + CUDA IPC is used, as the reference does. All ranks of a
+ * group must run with the same setting. */
+#define MCEP_FABRIC_HANDLE_INT32S 18
 
 typedef struct mcep_buffer mcep_buffer;
 typedef struct mcep_event mcep_event;
@@ -85,10 +93,15 @@ int mcep_buffer_is_roce(const mcep_buffer* buf);
 /* 1 when every active rank's memory is mapped (single rank: always 1);
  * mooncake-ep/include/mooncake_ep_buffer.h:143, `use_fast_path`. */
 int mcep_buffer_use_fast_path(const mcep_buffer* buf);
+/* 1 when the buffer was allocated in the fabric-handle mode (MC_USE_NVLINK_IPC=0
+ * and driver support, see MCEP_FABRIC_HANDLE_INT32S), 0 for cudaMalloc + CUDA IPC.
+ * mooncake-transfer-engine/src/transport/device/p2p_device_transport.cpp:40-60. */
+int mcep_buffer_uses_fabric_handles(const mcep_buffer* buf);
 
 /* MooncakeEpBuffer::get_ipc_handle (mooncake-ep/src/mooncake_ep_buffer.cpp:518-521):
- * writes MCEP_IPC_HANDLE_INT32S int32 to `out` (capacity in int32),
- * `*n_written` = 0 when P2P is disabled. */
+ * writes MCEP_IPC_HANDLE_INT32S int32 to `out` (capacity in int32; in fabric mode
+ * MCEP_FABRIC_HANDLE_INT32S, so pass room for 18), `*n_written` = 0 when P2P is
+ * disabled. */
 int mcep_buffer_get_ipc_handle(mcep_buffer* buf, int32_t* out, int capacity,
                                int* n_written);
 
@@ -147,6 +160,19 @@ int mcep_launch_deferred(mcep_buffer* const* bufs, int n);
  *                     phase of a call in one launch (default 1)
  *   "defer_launch"    1 = in-process groups: prepare calls, launch them together
  *                     with mcep_launch_deferred (default 0)
+ *   "graph_mode"      1 = calls of a group can be captured in a CUDA graph and
+ *                     replayed (default 0). The words ranks exchange carry the
+ *                     call's sequence number; by default it is a launch
+ *                     argument, which a replay would repeat. In graph mode the
+ *                     next number of each parity lives in device memory: the
+ *                     kernels read it, and a one-thread kernel after the call's
+ *                     last launch (in hook mode: launched by the hook) moves it
+ *                     on. Costs one tiny launch per call. A captured graph must
+ *                     hold an even number of dispatch calls and of combine calls
+ *                     (whole layers of two micro-batches, or an even number of
+ *                     layers), so that every replay starts on the parity it was
+ *                     captured on; every rank of the group must replay alike.
+ *                     Set it with nothing in flight, on every rank.
  * An unknown name is an error. */
 int mcep_buffer_set_option(mcep_buffer* buf, const char* name, int64_t value);
 
@@ -157,8 +183,9 @@ int mcep_buffer_set_option(mcep_buffer* buf, const char* name, int64_t value);
 int mcep_buffer_status(mcep_buffer* buf, int32_t* out, int n);
 
 /* Dispatch and combine calls this buffer has made (or adopted at a membership
- * refresh). No counterpart in the reference. */
-int mcep_buffer_call_counts(const mcep_buffer* buf, uint32_t* dispatch_calls,
+ * refresh); in graph mode read from the device, after waiting for it to go
+ * idle, so replayed graphs are counted. No counterpart in the reference. */
+int mcep_buffer_call_counts(mcep_buffer* buf, uint32_t* dispatch_calls,
                             uint32_t* combine_calls);
 
 /* Where the NEXT dispatch call of this buffer lands its rows: the packed

@@ -1300,11 +1300,23 @@ __device__ __forceinline__ void dispatch_body(const GroupDispatchParams& p, int 
     }
 }
 
+// Graph mode: a captured launch is replayed with the arguments it was captured
+// with, so the call's sequence number cannot be one of them; it is read from the
+// device word the host named (stable until the call's last kernel has finished:
+// the word of the other parity belongs to the other call that may be in flight).
+template <typename Params>
+__device__ __forceinline__ void resolve_seq(Params& p) {
+    if (p.seq_ptr != nullptr) p.seq = *reinterpret_cast<const volatile uint32_t*>(p.seq_ptr);
+}
+
+__global__ void ep_advance_seq_kernel(uint32_t* word) { *word += 2; }
+
 template <bool kFP8, bool kFused, int kPhases>
 __global__ void __launch_bounds__(512) ep_dispatch_kernel(GroupDispatchParams p) {
     extern __shared__ int smem_i32[];
     pdl_wait();
     pdl_launch_dependents();
+    resolve_seq(p);
     dispatch_body<kFP8, kFused, kPhases>(p, blockIdx.x, gridDim.x, smem_i32);
 }
 
@@ -1328,6 +1340,7 @@ __global__ void __launch_bounds__(kRowWarps * 32, 4) ep_dispatch_recv_kernel(Gro
     extern __shared__ int smem_i32[];
     pdl_wait();
     pdl_launch_dependents();
+    resolve_seq(p);
     MCEP_TRACE(1, 0);
     dispatch_recv_duty<kFP8>(p, blockIdx.x, gridDim.x, smem_i32);
 }
@@ -1500,6 +1513,7 @@ __global__ void __launch_bounds__(512) ep_combine_kernel(GroupCombineParams p) {
     extern __shared__ int smem_i32[];
     pdl_wait();
     pdl_launch_dependents();
+    resolve_seq(p);
     combine_body<kPhases>(p, blockIdx.x, gridDim.x, smem_i32);
 }
 
@@ -1681,9 +1695,9 @@ size_t dispatch_smem(const GroupDispatchParams& p, bool with_recv) {
 }  // namespace
 
 bool group_call_can_be_one_kernel(int T, int K, int E, int num_sms) {
-    // a small batch: one block per token plus the control block, resident at
-    // one block per SM
-    return can_fuse_layout(T, K, E, num_sms) && T + 1 <= num_sms;
+    // a small batch: one block per token plus the control block (the launcher
+    // falls back to two launches when that many blocks are not resident at once)
+    return can_fuse_layout(T, K, E, num_sms) && T + 1 <= 2 * num_sms;
 }
 
 cudaError_t launch_group_dispatch(const GroupDispatchParams& p, const LaunchCtx& ctx) {
@@ -1757,6 +1771,12 @@ cudaError_t launch_group_combine_reduce(const GroupCombineParams& p, const Launc
     auto k = ep_combine_kernel<2>;
     const int grid = persistent_grid(p.T, k, threads, 0, ctx);
     return launch("ep_combine_reduce", k, dim3(grid), dim3(threads), 0, ctx, p);
+}
+
+cudaError_t launch_advance_seq(uint32_t* word, const LaunchCtx& ctx) {
+    LaunchCtx plain = ctx;
+    plain.pdl = false;  // ordinary stream order: after everything the call launched
+    return launch("ep_advance_seq", ep_advance_seq_kernel, dim3(1), dim3(1), 0, plain, word);
 }
 
 // ---- in-process groups: all ranks in one cooperative launch ------------------------

@@ -131,6 +131,7 @@ struct GroupDispatchParams {
     size_t meta_off;            // side messages [L][R*M][meta_stride] of this parity
     int row_bytes, meta_stride;
     uint32_t seq;
+    const uint32_t* seq_ptr;    // graph mode: the call's sequence number lives in device memory (else null)
     WaitCfg wait;
     // scratch in the local workspace (per parity)
     uint64_t* res_cnt;          // [L*R] the control block's verdict per (expert, source)
@@ -169,6 +170,7 @@ struct GroupCombineParams {
     Words w;
     size_t cin_off;             // combine input [L][R*M][H] bf16 of this parity
     uint32_t seq;
+    const uint32_t* seq_ptr;    // graph mode (see GroupDispatchParams)
     WaitCfg wait;
     uint64_t* res_cflag;        // [R]
     unsigned* ticket;
@@ -188,6 +190,10 @@ cudaError_t launch_group_dispatch_multi(const GroupDispatchParams* params, int n
                                         const LaunchCtx& ctx);
 cudaError_t launch_group_combine_multi(const GroupCombineParams* params, int n,
                                        GroupCombineParams* dev_params, const LaunchCtx& ctx);
+
+// Graph mode: after the last kernel of a call, the word that holds the next
+// sequence number of that call's parity moves on by two.
+cudaError_t launch_advance_seq(uint32_t* word, const LaunchCtx& ctx);
 
 uint64_t kernel_launch_count();
 // Per-kernel device times: switch on, run, then drain "name launches total_ms" lines.

@@ -12,6 +12,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <functional>
 #include <memory>
@@ -76,7 +77,7 @@ struct Buffer {  // mooncake-ep/include/mooncake_ep_buffer.h:65-195
     bool p2p_enabled() const { return mcep_buffer_p2p_enabled(h) != 0; }
     bool use_fast_path() const { return mcep_buffer_use_fast_path(h) != 0; }
     std::vector<int32_t> get_ipc_handle() {
-        std::vector<int32_t> v(MCEP_IPC_HANDLE_INT32S);
+        std::vector<int32_t> v(MCEP_FABRIC_HANDLE_INT32S);  // room for either kind of handle
         int n = 0;
         check(mcep_buffer_get_ipc_handle(h, v.data(), (int)v.size(), &n));
         v.resize(n);
@@ -84,12 +85,14 @@ struct Buffer {  // mooncake-ep/include/mooncake_ep_buffer.h:65-195
     }
     void sync_nvlink_ipc_handles(const std::vector<std::vector<int32_t>>& handles,
                                  const std::vector<int32_t>& active_ranks_mask) {
-        std::vector<int32_t> flat((size_t)num_ranks * MCEP_IPC_HANDLE_INT32S, 0);
+        size_t per = MCEP_IPC_HANDLE_INT32S;
+        for (const auto& h : handles) per = std::max(per, h.size());
+        std::vector<int32_t> flat((size_t)num_ranks * per, 0);
         std::vector<int32_t> mask(num_ranks, 1);
         for (int r = 0; r < num_ranks && r < (int)handles.size(); ++r)
-            std::copy(handles[r].begin(), handles[r].end(), flat.begin() + (size_t)r * MCEP_IPC_HANDLE_INT32S);
+            std::copy(handles[r].begin(), handles[r].end(), flat.begin() + (size_t)r * per);
         for (int r = 0; r < num_ranks && r < (int)active_ranks_mask.size(); ++r) mask[r] = active_ranks_mask[r];
-        check(mcep_buffer_sync_nvlink_ipc_handles(h, flat.data(), MCEP_IPC_HANDLE_INT32S, mask.data()));
+        check(mcep_buffer_sync_nvlink_ipc_handles(h, flat.data(), (int)per, mask.data()));
     }
 
     // mooncake-ep/include/mooncake_ep_buffer.h:116-124

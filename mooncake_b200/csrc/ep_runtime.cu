@@ -5,6 +5,7 @@
 // of mooncake-transfer-engine/src/transport/device/p2p_device_transport.cpp.
 // No RDMA route, no CPU fallback: every path launches the kernels of
 // ep_kernels.cu or fails with an error.
+#include <cuda.h>  // types of the virtual-memory API only; entry points are looked up at run time
 #include <cuda_runtime.h>
 
 #include <cstdarg>
@@ -66,6 +67,128 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
 
+// ---- fabric-handle allocation (the reference's MC_USE_NVLINK_IPC=0 mode) -----------
+// mooncake-transfer-engine/src/transport/device/p2p_device_transport.cpp:40-60
+// (when it applies), :271-386 (allocation), :414-431 (export), :520-580 (import).
+// The symmetric buffer is then a cuMemCreate allocation that is exported as a
+// CUmemFabricHandle instead of a cudaIpcMemHandle_t. The driver entry points are
+// resolved through the runtime, so the library has no link-time dependency on
+// the driver and still loads on a machine without one.
+namespace {
+
+struct DriverApi {
+    CUresult (*DeviceGet)(CUdevice*, int) = nullptr;
+    CUresult (*DeviceGetAttribute)(int*, CUdevice_attribute, CUdevice) = nullptr;
+    CUresult (*MemGetAllocationGranularity)(size_t*, const CUmemAllocationProp*,
+                                           CUmemAllocationGranularity_flags) = nullptr;
+    CUresult (*MemCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*,
+                          unsigned long long) = nullptr;
+    CUresult (*MemRelease)(CUmemGenericAllocationHandle) = nullptr;
+    CUresult (*MemAddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+    CUresult (*MemAddressFree)(CUdeviceptr, size_t) = nullptr;
+    CUresult (*MemMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+    CUresult (*MemUnmap)(CUdeviceptr, size_t) = nullptr;
+    CUresult (*MemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+    CUresult (*MemExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType,
+                                           unsigned long long) = nullptr;
+    CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*,
+                                             CUmemAllocationHandleType) = nullptr;
+    bool ok = false;
+};
+
+template <typename F>
+bool driver_symbol(const char* name, F* fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult st;
+    if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &st) != cudaSuccess ||
+        st != cudaDriverEntryPointSuccess || p == nullptr) {
+        cudaGetLastError();
+        return false;
+    }
+    *fn = reinterpret_cast<F>(p);
+    return true;
+}
+
+const DriverApi& driver_api() {
+    static DriverApi api = [] {
+        DriverApi a;
+        a.ok = driver_symbol("cuDeviceGet", &a.DeviceGet) &&
+               driver_symbol("cuDeviceGetAttribute", &a.DeviceGetAttribute) &&
+               driver_symbol("cuMemGetAllocationGranularity", &a.MemGetAllocationGranularity) &&
+               driver_symbol("cuMemCreate", &a.MemCreate) && driver_symbol("cuMemRelease", &a.MemRelease) &&
+               driver_symbol("cuMemAddressReserve", &a.MemAddressReserve) &&
+               driver_symbol("cuMemAddressFree", &a.MemAddressFree) &&
+               driver_symbol("cuMemMap", &a.MemMap) && driver_symbol("cuMemUnmap", &a.MemUnmap) &&
+               driver_symbol("cuMemSetAccess", &a.MemSetAccess) &&
+               driver_symbol("cuMemExportToShareableHandle", &a.MemExportToShareableHandle) &&
+               driver_symbol("cuMemImportFromShareableHandle", &a.MemImportFromShareableHandle);
+        return a;
+    }();
+    return api;
+}
+
+// MC_USE_NVLINK_IPC=0 asks for fabric handles; they are used only where every
+// visible device supports them (the reference's supportFabricMem).
+bool fabric_requested_and_supported() {
+    const char* env = std::getenv("MC_USE_NVLINK_IPC");
+    if (env == nullptr || std::strcmp(env, "0") != 0) return false;
+    const DriverApi& d = driver_api();
+    if (!d.ok) return false;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return false;
+    }
+    for (int i = 0; i < n; ++i) {
+        CUdevice dev;
+        int supported = 0;
+        if (d.DeviceGet(&dev, i) != CUDA_SUCCESS ||
+            d.DeviceGetAttribute(&supported, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED, dev) !=
+                CUDA_SUCCESS ||
+            !supported)
+            return false;
+    }
+    return true;
+}
+
+struct FabricMapping {  // one mapped allocation: this rank's own, or an imported peer's
+    CUdeviceptr va = 0;
+    size_t size = 0;
+    CUmemGenericAllocationHandle handle = 0;
+};
+
+bool fabric_map(const DriverApi& d, CUmemGenericAllocationHandle handle, size_t size, size_t align,
+                int device, FabricMapping* out) {
+    CUdeviceptr va = 0;
+    if (d.MemAddressReserve(&va, size, align, 0, 0) != CUDA_SUCCESS) return false;
+    if (d.MemMap(va, size, 0, handle, 0) != CUDA_SUCCESS) {
+        d.MemAddressFree(va, size);
+        return false;
+    }
+    CUmemAccessDesc acc = {};
+    acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    acc.location.id = device;
+    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    if (d.MemSetAccess(va, size, &acc, 1) != CUDA_SUCCESS) {
+        d.MemUnmap(va, size);
+        d.MemAddressFree(va, size);
+        return false;
+    }
+    out->va = va, out->size = size, out->handle = handle;
+    return true;
+}
+
+void fabric_unmap(const DriverApi& d, FabricMapping* m) {
+    if (m->va) {
+        d.MemUnmap(m->va, m->size);
+        d.MemAddressFree(m->va, m->size);
+    }
+    if (m->handle) d.MemRelease(m->handle);
+    *m = FabricMapping();
+}
+
+}  // namespace
+
 struct mcep_event {
     cudaEvent_t ev = nullptr;
 };
@@ -91,6 +214,9 @@ struct mcep_buffer {
     std::vector<void*> peer_host;    // same, host copy
     std::vector<int32_t> available;  // host copy of the availability table
     std::vector<void*> ipc_opened;   // mappings to close
+    bool fabric = false;             // the buffer is a cuMemCreate allocation shared through fabric handles
+    FabricMapping own;               // fabric mode: this rank's allocation
+    std::vector<FabricMapping> fabric_peers;
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ev_a = nullptr, ev_b = nullptr;  // reusable ordering events
     uint32_t dseq = 0, cseq = 0;     // dispatch / combine calls issued so far
@@ -105,6 +231,11 @@ struct mcep_buffer {
 
     // In-process groups: calls are prepared but not launched until
     // mcep_launch_deferred starts all ranks' work in one launch.
+    // Graph mode: the sequence number of the next call of each kind and parity
+    // lives in device memory ([0..1] dispatch, [2..3] combine; parity = index & 1),
+    // so that a captured call can be replayed (see mcep_buffer_set_option).
+    bool graph_mode = false;
+    uint32_t* dev_next_seq = nullptr;
     bool defer = false;
     struct Pending {
         int kind = 0;                // 0 none, 1 dispatch, 2 combine
@@ -119,8 +250,10 @@ struct mcep_buffer {
     struct DispatchRecord {
         const void* key = nullptr;  // the handle's src_info tensor
         uint32_t seq = 0;
+        uint64_t stamp = 0;         // host-side order of the dispatch calls (the newer record wins)
         int T = 0, K = 0, E = 0, M = 0, H = 0;
     } record[2];
+    uint64_t record_clock = 0;
 };
 
 namespace {
@@ -153,6 +286,11 @@ Geometry geometry(int R, int E, int M, int H, bool fp8) {
 
 int64_t to_ns(int64_t timeout_us) { return timeout_us < 0 ? -1 : timeout_us * 1000; }
 
+// Kernels of one call are chained with programmatic dependent launch - except
+// while the stream is being captured into a graph, where plain dependencies are
+// recorded.
+bool chain_with_pdl(const mcep_buffer* b, cudaStream_t stream);
+
 bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 int order_after(cudaStream_t later, cudaStream_t earlier, cudaEvent_t ev) {
@@ -170,6 +308,18 @@ int check_connected(const mcep_buffer* b) {
     return MCEP_OK;
 }
 
+}  // namespace
+
+namespace {
+bool chain_with_pdl(const mcep_buffer* b, cudaStream_t stream) {
+    if (!b->pdl) return false;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return st == cudaStreamCaptureStatusNone;
+}
 }  // namespace
 
 extern "C" {
@@ -231,7 +381,32 @@ int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int
     CK(cudaEventCreateWithFlags(&b->ev_a, cudaEventDisableTiming));
     CK(cudaEventCreateWithFlags(&b->ev_b, cudaEventDisableTiming));
     const size_t total = kHeaderRegion + align_up((size_t)num_ep_buffer_bytes, 256);
-    CK(cudaMalloc(reinterpret_cast<void**>(&b->base), total));
+    if (num_ranks > 1 && b->p2p_enabled && fabric_requested_and_supported()) {
+        // the reference's fabric mode: a cuMemCreate allocation with a fabric handle
+        const DriverApi& d = driver_api();
+        CUmemAllocationProp prop = {};
+        prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        prop.location.id = b->device;
+        prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_FABRIC;
+        size_t gran = 0;
+        CUmemGenericAllocationHandle h = 0;
+        if (d.MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS &&
+            gran > 0) {
+            const size_t size = align_up(total, gran);
+            if (d.MemCreate(&h, size, &prop, 0) == CUDA_SUCCESS) {
+                if (fabric_map(d, h, size, gran, b->device, &b->own)) {
+                    b->fabric = true;
+                    b->base = reinterpret_cast<char*>(b->own.va);
+                } else {
+                    d.MemRelease(h);
+                }
+            }
+        }
+        if (!b->fabric)
+            fprintf(stderr, "[mcep] rank %d: fabric-handle allocation failed, using cudaMalloc + CUDA IPC\n", rank);
+    }
+    if (!b->fabric) CK(cudaMalloc(reinterpret_cast<void**>(&b->base), total));
     CK(cudaMemset(b->base, 0, total));
     CK(cudaMalloc(reinterpret_cast<void**>(&b->workspace), kWorkspaceBytes));
     CK(cudaMemset(b->workspace, 0, kWorkspaceBytes));
@@ -246,6 +421,7 @@ int mcep_buffer_create(int rank, int num_ranks, int64_t num_ep_buffer_bytes, int
 #undef CK
     // workspace: [status 256 B][parity 0 scratch][parity 1 scratch]
     b->status = reinterpret_cast<int32_t*>(b->workspace);
+    b->dev_next_seq = reinterpret_cast<uint32_t*>(b->workspace + 256 + 192);  // beside parity 0's tickets
     const size_t words = (size_t)MCEP_MAX_EXPERTS * sizeof(uint64_t);
     const size_t small = (size_t)(MCEP_MAX_EXPERTS + 64) * sizeof(int32_t);
     const size_t half = (kWorkspaceBytes - 256) / 2;
@@ -282,7 +458,12 @@ int mcep_buffer_destroy(mcep_buffer* b) {
     if (cur != b->device) cudaSetDevice(b->device);
     cudaDeviceSynchronize();
     for (void* p : b->ipc_opened) cudaIpcCloseMemHandle(p);
-    if (b->base) cudaFree(b->base);
+    if (b->fabric) {
+        for (auto& m : b->fabric_peers) fabric_unmap(driver_api(), &m);
+        fabric_unmap(driver_api(), &b->own);
+    } else if (b->base) {
+        cudaFree(b->base);
+    }
     if (b->workspace) cudaFree(b->workspace);
     if (b->peer_dev) cudaFree(b->peer_dev);
     if (b->ev_a) cudaEventDestroy(b->ev_a);
@@ -298,6 +479,7 @@ int mcep_buffer_ibgda_disabled(const mcep_buffer*) { return 1; }
 int mcep_buffer_p2p_enabled(const mcep_buffer* b) { return b && b->p2p_enabled ? 1 : 0; }
 int mcep_buffer_is_roce(const mcep_buffer*) { return 0; }
 int mcep_buffer_use_fast_path(const mcep_buffer* b) { return b && b->all_peers ? 1 : 0; }
+int mcep_buffer_uses_fabric_handles(const mcep_buffer* b) { return b && b->fabric ? 1 : 0; }
 
 // The words ranks exchange carry the number of the call they belong to, so all
 // ranks of a group must count their calls alike. A rank that sat out some calls
@@ -305,7 +487,29 @@ int mcep_buffer_use_fast_path(const mcep_buffer* b) { return b && b->all_peers ?
 // membership is refreshed: every rank leaves its two counters in its own
 // symmetric memory before the handles are exchanged, reads every mapped peer's
 // afterwards and continues from the largest.
+// Graph mode: the device words are the truth (replayed graphs advance them, the
+// host never hears of it). next[par] = sequence number the next call of that
+// parity will carry, so the last call made carried max(next[0], next[1]) - 2.
+static int read_device_seq(mcep_buffer* b) {
+    if (!b->graph_mode) return MCEP_OK;
+    uint32_t w[4];
+    MCEP_CUDA(cudaMemcpy(w, b->dev_next_seq, sizeof(w), cudaMemcpyDeviceToHost));
+    b->dseq = (w[0] > w[1] ? w[0] : w[1]) - 2;
+    b->cseq = (w[2] > w[3] ? w[2] : w[3]) - 2;
+    return MCEP_OK;
+}
+
+static int write_device_seq(mcep_buffer* b) {
+    uint32_t w[4];
+    const uint32_t d = b->dseq + 1, c = b->cseq + 1;  // the next calls' numbers
+    w[d & 1] = d, w[(d + 1) & 1] = d + 1;
+    w[2 + (c & 1)] = c, w[2 + ((c + 1) & 1)] = c + 1;
+    MCEP_CUDA(cudaMemcpy(b->dev_next_seq, w, sizeof(w), cudaMemcpyHostToDevice));
+    return MCEP_OK;
+}
+
 static int publish_seq(mcep_buffer* b) {
+    if (int rc = read_device_seq(b)) return rc;
     const uint32_t pub[2] = {b->dseq, b->cseq};
     MCEP_CUDA(cudaMemcpy(b->base + kPubSeqOff, pub, sizeof(pub), cudaMemcpyHostToDevice));
     return MCEP_OK;
@@ -328,6 +532,7 @@ static int adopt_largest_seq(mcep_buffer* b) {
     }
     b->dseq = d;
     b->cseq = c;
+    if (b->graph_mode) return write_device_seq(b);
     return MCEP_OK;
 }
 
@@ -340,6 +545,23 @@ int mcep_buffer_get_ipc_handle(mcep_buffer* b, int32_t* out, int capacity, int* 
                   "handle size");
     MCEP_CUDA(cudaDeviceSynchronize());
     if (int rc = publish_seq(b)) return rc;
+    if (b->fabric) {
+        // [CUmemFabricHandle 64 B | size 8 B] as 18 int32, the reference's serialisation
+        // (p2p_device_transport.cpp:61-75); the length tells the importer which kind it is
+        MCEP_REQUIRE(capacity >= MCEP_FABRIC_HANDLE_INT32S);
+        CUmemFabricHandle fh;
+        if (driver_api().MemExportToShareableHandle(&fh, b->own.handle, CU_MEM_HANDLE_TYPE_FABRIC, 0) !=
+            CUDA_SUCCESS)
+            return fail(MCEP_ERR_CUDA, "Failed: CUDA error %s:%d 'cuMemExportToShareableHandle(FABRIC)'",
+                        __FILE__, __LINE__);
+        static_assert(sizeof(CUmemFabricHandle) + sizeof(uint64_t) == MCEP_FABRIC_HANDLE_INT32S * sizeof(int32_t),
+                      "fabric handle size");
+        const uint64_t size = b->own.size;
+        std::memcpy(out, &fh, sizeof(fh));
+        std::memcpy(reinterpret_cast<char*>(out) + sizeof(fh), &size, sizeof(size));
+        *n_written = MCEP_FABRIC_HANDLE_INT32S;
+        return MCEP_OK;
+    }
     cudaIpcMemHandle_t h;
     MCEP_CUDA(cudaIpcGetMemHandle(&h, b->base));
     std::memcpy(out, &h, sizeof(h));
@@ -366,6 +588,39 @@ int mcep_buffer_sync_nvlink_ipc_handles(mcep_buffer* b, const int32_t* handles, 
     MCEP_CUDA(cudaDeviceSynchronize());
     for (void* p : b->ipc_opened) cudaIpcCloseMemHandle(p);
     b->ipc_opened.clear();
+    for (auto& m : b->fabric_peers) fabric_unmap(driver_api(), &m);
+    b->fabric_peers.clear();
+    if (b->fabric) {
+        MCEP_REQUIRE(n_per_handle >= MCEP_FABRIC_HANDLE_INT32S);
+        const DriverApi& d = driver_api();
+        for (int r = 0; r < b->num_ranks; ++r) {
+            if (r == b->rank) continue;
+            b->peer_host[r] = nullptr;
+            b->available[r] = 0;
+            if (mask && mask[r] == 0) continue;
+            CUmemFabricHandle fh;
+            uint64_t size = 0;
+            const char* src = reinterpret_cast<const char*>(handles + (size_t)r * n_per_handle);
+            std::memcpy(&fh, src, sizeof(fh));
+            std::memcpy(&size, src + sizeof(fh), sizeof(size));
+            CUmemGenericAllocationHandle h = 0;
+            FabricMapping m;
+            if (size == 0 || d.MemImportFromShareableHandle(&h, &fh, CU_MEM_HANDLE_TYPE_FABRIC) != CUDA_SUCCESS) {
+                fprintf(stderr, "[mcep] rank %d: cuMemImportFromShareableHandle(FABRIC) failed for rank %d\n",
+                        b->rank, r);
+                continue;
+            }
+            if (!fabric_map(d, h, (size_t)size, 0, b->device, &m)) {
+                d.MemRelease(h);
+                fprintf(stderr, "[mcep] rank %d: cannot map rank %d's fabric allocation\n", b->rank, r);
+                continue;
+            }
+            b->fabric_peers.push_back(m);
+            b->peer_host[r] = reinterpret_cast<void*>(m.va);
+            b->available[r] = 1;
+        }
+        return publish_peers(b, mask);
+    }
     int device_count = 1;
     if (cudaGetDeviceCount(&device_count) != cudaSuccess || device_count < 1) {
         cudaGetLastError();
@@ -446,6 +701,15 @@ int mcep_buffer_set_option(mcep_buffer* b, const char* name, int64_t value) {
         b->one_kernel = value != 0;
     } else if (!std::strcmp(name, "defer_launch")) {
         b->defer = value != 0;
+    } else if (!std::strcmp(name, "graph_mode")) {
+        MCEP_CUDA(cudaDeviceSynchronize());
+        if (value != 0 && !b->graph_mode) {
+            if (int rc = write_device_seq(b)) return rc;
+            b->graph_mode = true;
+        } else if (value == 0 && b->graph_mode) {
+            if (int rc = read_device_seq(b)) return rc;
+            b->graph_mode = false;
+        }
     } else {
         return fail(MCEP_ERR_INVALID, "Failed: unknown option '%s'", name);
     }
@@ -458,8 +722,12 @@ int mcep_buffer_status(mcep_buffer* b, int32_t* out, int n) {
     return MCEP_OK;
 }
 
-int mcep_buffer_call_counts(const mcep_buffer* b, uint32_t* dispatch_calls, uint32_t* combine_calls) {
+int mcep_buffer_call_counts(mcep_buffer* b, uint32_t* dispatch_calls, uint32_t* combine_calls) {
     MCEP_REQUIRE(b != nullptr && dispatch_calls != nullptr && combine_calls != nullptr);
+    if (b->graph_mode) {
+        MCEP_CUDA(cudaDeviceSynchronize());
+        if (int rc = read_device_seq(b)) return rc;
+    }
     *dispatch_calls = b->dseq;
     *combine_calls = b->cseq;
     return MCEP_OK;
@@ -571,7 +839,8 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
         if (int rc = order_after(stream, compute, b->ev_a)) return rc;
 
     mcep::LaunchCtx first{stream, b->num_sms, false};
-    mcep::LaunchCtx next{stream, b->num_sms, b->pdl};
+    const bool pdl = chain_with_pdl(b, stream) && chain_with_pdl(b, compute);
+    mcep::LaunchCtx next{stream, b->num_sms, pdl};
 
     const bool fused = mcep::can_fuse_layout(T, K, E, b->num_sms) && b->fuse_layout;
     if (!fused) {
@@ -597,7 +866,7 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
         dp.recv_count = a->packed_recv_count, dp.layout_range = a->packed_recv_layout_range;
         dp.rowmap = sc.rowmap;
         auto& rec = b->record[par];
-        rec.key = a->packed_recv_src_info, rec.seq = seq;
+        rec.key = a->packed_recv_src_info, rec.seq = seq, rec.stamp = ++b->record_clock;
         rec.T = T, rec.K = K, rec.E = E, rec.M = M, rec.H = H;
         MCEP_CUDA(mcep::launch_direct_dispatch(dp, fused ? first : next));
         if (a->return_recv_hook) {
@@ -620,6 +889,8 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     p.rx_off = (size_t)(area - b->base), p.meta_off = p.rx_off + g.meta_off;
     p.row_bytes = g.row_bytes, p.meta_stride = g.meta_stride;
     p.seq = seq;
+    uint32_t* seq_word = b->graph_mode ? b->dev_next_seq + par : nullptr;
+    p.seq_ptr = seq_word;
     p.wait.active_ranks = a->active_ranks, p.wait.timeout_ns = to_ns(a->timeout_us);
     p.wait.hard_timeout_ns = b->hard_timeout_ns, p.wait.status = b->status;
     p.res_cnt = sc.res_cnt, p.res_dflag = sc.res_dflag, p.ticket = sc.send_ticket;
@@ -632,16 +903,15 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     p.copy_rows = (a->packed_recv_x != static_cast<void*>(area));
 
     auto& rec = b->record[par];
-    rec.key = a->packed_recv_src_info, rec.seq = seq;
+    rec.key = a->packed_recv_src_info, rec.seq = seq, rec.stamp = ++b->record_clock;
     rec.T = T, rec.K = K, rec.E = E, rec.M = M, rec.H = H;
 
-    const bool pdl = b->pdl;
     const int num_sms = b->num_sms;
     // Small batches, rows in place, no hook: one launch does it all.
     bool one_kernel = fused && !p.copy_rows && !a->return_recv_hook && b->one_kernel &&
                       mcep::group_call_can_be_one_kernel(T, K, E, num_sms);
     if (b->defer) {
-        MCEP_REQUIRE(!a->async_finish);
+        MCEP_REQUIRE(!a->async_finish && !b->graph_mode);
         b->pending.kind = 1, b->pending.phases = one_kernel ? 3 : 1, b->pending.d = p;
         b->pending.then_second = !one_kernel && !a->return_recv_hook;
         b->pending.stream = compute;
@@ -667,9 +937,10 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     }
     if (!one_kernel) MCEP_CUDA(mcep::launch_group_dispatch_send(p, fused ? first : next));
     auto recv = [=](cudaStream_t s, bool chained) -> int {
-        if (one_kernel) return MCEP_OK;
         mcep::LaunchCtx c0{s, num_sms, chained && pdl};
-        MCEP_CUDA(mcep::launch_group_dispatch_recv(p, c0));
+        if (!one_kernel) MCEP_CUDA(mcep::launch_group_dispatch_recv(p, c0));
+        // graph mode: the call is over, its parity's word moves on
+        if (seq_word) MCEP_CUDA(mcep::launch_advance_seq(seq_word, c0));
         return MCEP_OK;
     };
 
@@ -720,7 +991,7 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
 
     cudaStream_t compute = reinterpret_cast<cudaStream_t>(a->compute_stream);
     cudaStream_t stream = a->async_finish ? b->comm_stream : compute;
-    const bool pdl = b->pdl;
+    const bool pdl = chain_with_pdl(b, stream) && chain_with_pdl(b, compute);
     const int num_sms = b->num_sms;
 
     if (!group) {
@@ -740,7 +1011,7 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
             const mcep_buffer::DispatchRecord* rec = nullptr;
             for (int i = 0; i < 2; ++i) {
                 const auto& c = b->record[i];
-                if (c.key != nullptr && c.key == a->src_info && (rec == nullptr || c.seq > rec->seq))
+                if (c.key != nullptr && c.key == a->src_info && (rec == nullptr || c.stamp > rec->stamp))
                     rec = &c;
             }
             if (rec && rec->T == T && rec->K == K && rec->E == E && rec->M == M && rec->H == H)
@@ -784,7 +1055,7 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
     const mcep_buffer::DispatchRecord* rec = nullptr;
     for (int i = 0; i < 2; ++i) {
         const auto& c = b->record[i];
-        if (c.key != nullptr && c.key == a->src_info && (rec == nullptr || c.seq > rec->seq)) rec = &c;
+        if (c.key != nullptr && c.key == a->src_info && (rec == nullptr || c.stamp > rec->stamp)) rec = &c;
     }
     if (rec == nullptr)
         return fail(MCEP_ERR_STATE,
@@ -813,6 +1084,8 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
     p.w = words_of(0, par);
     p.cin_off = kHeaderRegion + (size_t)par * g.parity_bytes + g.darea_bytes;
     p.seq = seq;
+    uint32_t* seq_word = b->graph_mode ? b->dev_next_seq + 2 + par : nullptr;
+    p.seq_ptr = seq_word;
     p.wait.active_ranks = a->active_ranks, p.wait.timeout_ns = to_ns(a->timeout_us);
     p.wait.hard_timeout_ns = b->hard_timeout_ns, p.wait.status = b->status;
     p.res_cflag = b->scratch[par].res_cflag, p.ticket = b->scratch[par].publish_ticket;
@@ -820,6 +1093,7 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
 
     const bool one_kernel = !a->return_recv_hook && b->one_kernel &&
                             mcep::group_call_can_be_one_kernel(T, K, E, num_sms);
+    MCEP_REQUIRE(!(b->defer && b->graph_mode));
     if (b->defer && !a->return_recv_hook) {
         // The publish phase waits for nobody and can be launched rank by rank,
         // the reduce phase only once every rank has published; both phases in one
@@ -835,9 +1109,9 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
     else
         MCEP_CUDA(mcep::launch_group_combine_publish(p, first));
     auto reduce = [=](cudaStream_t s, bool chained) -> int {
-        if (one_kernel) return MCEP_OK;
         mcep::LaunchCtx c0{s, num_sms, chained && pdl};
-        MCEP_CUDA(mcep::launch_group_combine_reduce(p, c0));
+        if (!one_kernel) MCEP_CUDA(mcep::launch_group_combine_reduce(p, c0));
+        if (seq_word) MCEP_CUDA(mcep::launch_advance_seq(seq_word, c0));
         return MCEP_OK;
     };
 

@@ -65,6 +65,7 @@ def _load() -> ctypes.CDLL:
         "mcep_buffer_p2p_enabled": (i32, [vp]),
         "mcep_buffer_is_roce": (i32, [vp]),
         "mcep_buffer_use_fast_path": (i32, [vp]),
+        "mcep_buffer_uses_fabric_handles": (i32, [vp]),
         "mcep_buffer_get_ipc_handle": (i32, [vp, _c.POINTER(_c.c_int32), i32, _c.POINTER(i32)]),
         "mcep_buffer_sync_nvlink_ipc_handles": (i32, [vp, _c.POINTER(_c.c_int32), i32,
                                                       _c.POINTER(_c.c_int32)]),
@@ -225,10 +226,15 @@ class Buffer:
     def use_fast_path(self) -> bool:
         return bool(_lib.mcep_buffer_use_fast_path(self._h))
 
+    def uses_fabric_handles(self) -> bool:
+        """True when the buffer is shared through fabric handles (MC_USE_NVLINK_IPC=0
+        and driver support) rather than CUDA IPC handles."""
+        return bool(_lib.mcep_buffer_uses_fabric_handles(self._h))
+
     def get_ipc_handle(self) -> List[int]:
-        out = (_c.c_int32 * 16)()
+        out = (_c.c_int32 * 18)()  # 16 for a CUDA IPC handle, 18 for a fabric handle + size
         n = _c.c_int(0)
-        _check(_lib.mcep_buffer_get_ipc_handle(self._h, out, 16, _c.byref(n)))
+        _check(_lib.mcep_buffer_get_ipc_handle(self._h, out, 18, _c.byref(n)))
         return list(out[: n.value])
 
     def sync_nvlink_ipc_handles(self, remote_handles: List[List[int]],

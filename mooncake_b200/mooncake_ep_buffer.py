@@ -19,6 +19,8 @@ and error behaviour. What is different underneath:
   symmetric tensor the next `combine(..., zero_copy=True)` reads (the reference
   documents it, docs/source/design/mooncake-ep.md:165-167, and rejects it,
   :551,680);
+* calls can be captured in CUDA graphs after `buffer.runtime.set_option("graph_mode", 1)`
+  (include/mcep.h);
 * the bootstrap only all-gathers the 64-byte memory handles
   (reference :271-285); the RDMA metadata exchange (:188-264) does not exist.
 """
@@ -31,6 +33,7 @@ import torch
 import torch.distributed as dist
 
 from . import ep
+
 
 def _stream_ptr() -> int:
     return int(torch.cuda.current_stream().cuda_stream)

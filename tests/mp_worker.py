@@ -33,6 +33,10 @@ def run_case(cfg, group, rank, R, buf_cache):
     if key not in buf_cache:
         buf_cache.clear()
         buf_cache[key] = Buffer(group, nbytes)
+        if rank == 0:
+            print("symmetric buffer shared through "
+                  + ("fabric handles" if buf_cache[key].runtime.uses_fabric_handles() else "CUDA IPC handles"),
+                  flush=True)
     buf = buf_cache[key]
     if cfg.get("refresh_members"):
         # membership refresh (Buffer.update_ep_member): every rank re-exports and
@@ -48,6 +52,8 @@ def run_case(cfg, group, rank, R, buf_cache):
     ar = torch.tensor(active, dtype=torch.int32, device="cuda")
     if cfg.get("check") == "properties":
         return run_full_size_case(cfg, buf, rank, R, xs, idxs, ws, x, idx, w, ar)
+    if cfg.get("graph"):
+        return run_graph_case(cfg, buf, rank, R, xs, idxs, ws, x, idx, w, ar)
     want = ora.dispatch(xs, idxs, M, E, cfg["fp8"], active=active)[rank]
     for rep in range(cfg.get("reps", 2)):  # twice: words, tickets and parities are reused
         mode = cfg.get("mode", "sync")
@@ -104,6 +110,52 @@ def run_case(cfg, group, rank, R, buf_cache):
             err = float((out.cpu().float() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
             assert err < 2e-2, f"combine rel err {err}"
         assert buf.runtime.status() == 0, "device status word set"
+
+
+def run_graph_case(cfg, buf, rank, R, xs, idxs, ws, x, idx, w, ar):
+    """Two layers captured in a CUDA graph on every rank ("graph_mode": the call's
+    sequence number lives in device memory) and replayed with rescaled inputs.
+    With a stale number a rank would take its peers' words of the previous replay
+    for the current ones and read rows before they are written."""
+    M, E, H = cfg["M"], cfg["E"], cfg["H"]
+    L = E // R
+    torch.cuda.synchronize()
+    dist.barrier()
+    buf.runtime.set_option("graph_mode", 1)
+
+    def layer():
+        recv, cnt, handle, _, _ = buf.dispatch(x, idx, ar, M, E, 5_000_000, use_fp8=False)
+        y = mock_expert(recv, rank, L)
+        out, _, _ = buf.combine(y, idx, w, ar, 5_000_000, handle)
+        return cnt, out
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        layer(), layer()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+        results = [layer(), layer()]
+    want = ora.dispatch(xs, idxs, M, E, False)[rank]
+    f = 1.0 + idxs[rank].clamp_min(0).float() / 16.0
+    keep = (idxs[rank] >= 0)
+    for rep in range(4):
+        scale = float(rep + 1)
+        x.copy_((xs[rank].float() * scale).to(torch.bfloat16))
+        g.replay()
+        torch.cuda.synchronize()
+        ref = (xs[rank].float() * scale).to(torch.bfloat16).float() * (ws[rank] * f * keep).sum(dim=1, keepdim=True)
+        for cnt, out in results:
+            assert torch.equal(cnt.cpu(), want["recv_count"]), "recv_count"
+            err = float((out.cpu().float() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+            assert err < 2e-2, f"replay {rep}: combine rel err {err}"
+    assert buf.runtime.status() == 0, "device status word set"
+    torch.cuda.synchronize()
+    dist.barrier()
+    buf.runtime.set_option("graph_mode", 0)
 
 
 def run_full_size_case(cfg, buf, rank, R, xs, idxs, ws, x, idx, w, ar):

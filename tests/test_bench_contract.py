@@ -53,3 +53,52 @@ def test_reference_arm_covers_all_ranks_work_in_a_group():
     d = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][0])
     assert d["n_gpus"] == 2 and d["config"]["ranks"] == 2
     assert abs(d["value"] - 2 * 16 / (d["ms_per_step"] / 1e3)) < 1e-6 * d["value"]
+
+
+def _bench_module():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_nvlink_bytes_come_from_the_routing_of_all_ranks():
+    """The NVLink roofline is the busiest GPU's ingress or egress, from what every
+    rank actually routes: for a routing that sends everything to rank 0's experts
+    it is rank 0's ingress, not the uniform expectation."""
+    import torch
+    b = _bench_module()
+    w = dict(T=8, H=4096, E=8, K=2, fp8=False, routing="uniform", name="c5", desc="")
+    R, L = 4, 2
+    idx_all = [torch.tensor([[0, 1]] * 8) for _ in range(R)]          # everybody picks experts 0 and 1
+    nv = b.nvlink_bytes(w, R, idx_all=idx_all)
+    remote_in_rank0 = 3 * 8 * 2                                      # three other ranks, 8 tokens, 2 picks
+    assert nv["selections_remote_max_gpu"] == remote_in_rank0
+    assert nv["dispatch_bytes_max_gpu"] == remote_in_rank0 * 2 * 4096
+    assert nv["combine_bytes_max_gpu"] == remote_in_rank0 * 2 * 4096
+    assert abs(nv["roofline_us"] - 2 * remote_in_rank0 * 8192 / 900e9 * 1e6) < 1e-9
+    # an inactive rank neither sends nor receives
+    nv2 = b.nvlink_bytes(w, R, inactive=3, idx_all=idx_all)
+    assert nv2["selections_remote_max_gpu"] == 2 * 8 * 2
+    # fp8 dispatch payload follows the reference's accounting: H + 4*H/128 + 16
+    w8 = dict(w, fp8=True)
+    assert b.nvlink_bytes(w8, R, idx_all=idx_all)["dispatch_bytes_max_gpu"] == remote_in_rank0 * (4096 + 128 + 16)
+    # masked entries move nothing
+    idx_masked = [torch.tensor([[0, -1]] * 8) for _ in range(R)]
+    assert b.nvlink_bytes(w, R, idx_all=idx_masked)["selections_remote_max_gpu"] == 3 * 8
+
+
+def test_both_arms_spell_the_workload_the_same_way():
+    b = _bench_module()
+
+    class A:
+        inactive_rank = -1
+    w = dict(b.WORKLOADS["c2"], name="c2")
+    cfg = b.config_of(w, 8, A())
+    assert set(cfg) == {"workload", "tokens_per_rank", "hidden", "experts", "experts_per_rank", "topk",
+                        "ranks", "routing", "dispatch_payload", "inactive_rank"}
+    assert cfg["experts_per_rank"] == 32 and cfg["dispatch_payload"] == "fp8_e4m3"
+    p = _run(["--steps", "1", "--warmup", "1"])
+    d = json.loads([l for l in p.stdout.splitlines() if l.startswith("{")][0])
+    assert set(d["config"]) == set(cfg)

@@ -34,6 +34,8 @@ def _cases(R):
                                           zero_copy=True, mode="hook"),
         "decode_fp8_caller_recv_x": dict(T=128, M=128, H=7168, E=256, K=8, fp8=True, seed=7,
                                          recv_in_place=False),
+        # two layers captured in a CUDA graph on every rank and replayed
+        "graph_replay_bf16": dict(T=96, M=128, H=2048, E=32, K=4, fp8=False, seed=10, graph=True),
         # config 5's largest point, and config 3 at its full 4096 tokens per rank
         # (checked through properties, the oracle does not finish these in seconds)
         "mixtral_t4096": dict(T=4096, M=4096, H=4096, E=8, K=2, fp8=False, check="properties"),
@@ -51,21 +53,40 @@ def _cases(R):
     return c
 
 
+def test_fabric_handle_mode_two_gpus():
+    """MC_USE_NVLINK_IPC=0 (the reference's switch,
+    mooncake-transfer-engine/src/transport/device/p2p_device_transport.cpp:40-43):
+    where the driver supports fabric handles the symmetric buffer is a
+    cuMemCreate allocation exported as a CUmemFabricHandle; elsewhere the request
+    is ignored, as the reference does. Either way the layer must match the oracle
+    (the worker's log says which kind of handle was exchanged)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cases = {k: v for k, v in _cases(2).items() if k in ("c1_bf16", "decode_fp8", "ragged", "masked_last_rank",
+                                                         "rejoined_after_refresh")}
+    _run_workers(2, cases, {"MC_USE_NVLINK_IPC": "0"}, "multi_gpu_parity_fabric_r2.log", port=29640)
+
+
 @pytest.mark.parametrize("R", [2, 4, 8])
 def test_multi_gpu_parity(R):
     if torch.cuda.device_count() < R:
         pytest.skip(f"needs {R} GPUs")
+    _run_workers(R, _cases(R), {}, f"multi_gpu_parity_r{R}.log", port=29620 + R)
+
+
+def _run_workers(R, cases, extra_env, log_name, port):
     env = dict(os.environ)
-    env["MCEP_TEST_CASES"] = json.dumps(_cases(R))
+    env.update(extra_env)
+    env["MCEP_TEST_CASES"] = json.dumps(cases)
     env["NCCL_NVLS_ENABLE"] = "0"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={R}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29620 + R),
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(ROOT, "tests", "mp_worker.py")]
     p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     out = p.stdout + p.stderr
     log_dir = os.environ.get("MCEP_TEST_LOG_DIR", "")
     if os.path.isdir(log_dir):  # keep the whole log of the child processes
-        with open(os.path.join(log_dir, f"multi_gpu_parity_r{R}.log"), "w") as f:
+        with open(os.path.join(log_dir, log_name), "w") as f:
             f.write(out)
     lines = [l for l in out.splitlines() if "FAILED" in l or "Error" in l or "assert" in l.lower()]
     assert p.returncode == 0, "\n".join(lines[-30:]) + "\n" + out[-1500:]
