@@ -333,6 +333,7 @@ class Layer:
         if self.inactive >= 0:
             self.active[self.inactive] = 0
         self.i_am_out = rank == self.inactive
+        self.rendezvous_launches = 0
         self.timeout_us = 2_000_000
         nbytes = Buffer.get_ep_buffer_size_hint(self.M, H, R, E) if (R > 1 or args.force_staged) else 0
         self.buf = Buffer(group, nbytes)
@@ -393,7 +394,15 @@ def timed_steps(layer, n_steps, n_warm, flush, sync, hide_host):
 
     def align():
         if R > 1:
-            dist.all_reduce(sync)  # device-side rendezvous, keeps the ranks' steps aligned
+            # rendezvous of the ranks' streams: a collective keeps the hosts in step but
+            # completes a few microseconds apart on different ranks, so the library's own
+            # device-side barrier (every rank leaves within about one NVLink latency of the
+            # others) follows it for the ranks that take part in the exchange
+            dist.all_reduce(sync)
+            if not layer.i_am_out:
+                layer.buf.runtime.barrier(torch.cuda.current_stream().cuda_stream,
+                                          layer.active.data_ptr())
+                layer.rendezvous_launches += 1
 
     def step(ev):
         if layer.i_am_out:
@@ -508,9 +517,12 @@ def run_ours(args):
     if sampler:
         sampler.start()
     launches0 = ep.kernel_launch_count()
+    layer.rendezvous_launches = 0
     td, tc, t_wall, step = timed_steps(layer, K_steps, warm, flush, sync_word, hide_host=True)
-    # launches of the timed steps alone (the warm-up steps launch the same kernels)
-    launches = (ep.kernel_launch_count() - launches0) * K_steps // (K_steps + warm)
+    # launches of the timed steps alone (the warm-up steps launch the same kernels); the
+    # rendezvous barrier between the event pairs is the bench's, not the hot path's
+    launches = ((ep.kernel_launch_count() - launches0 - layer.rendezvous_launches)
+                * K_steps // (K_steps + warm))
     main = summarise(td, tc, dev, R)
     ms_per_step = main["us_per_layer"] * 1e-3
 
@@ -608,6 +620,7 @@ def run_ours(args):
             v["share"] = v["avg_us"] * v["launches_per_step"] / tot
         return kern
 
+    ktimes.pop("ep_barrier", None)  # the rendezvous between the timed calls
     kern = kernel_table(ktimes, n_k, alg)
     dom = max(kern, key=lambda k: kern[k]["share"]) if kern else None
     traffic = None
@@ -702,9 +715,10 @@ def run_ours(args):
         "method": {"l2": ("NOT FLUSHED (diagnosis run)" if args.no_flush else
                           f"flushed before every dispatch and every combine ({L2_FLUSH_BYTES >> 20} MiB write)"),
                    "timing": "CUDA events around Buffer.dispatch and around Buffer.combine on the calling "
-                             "stream; a fixed device-side idle period is queued ahead of each timed call "
-                             "so the host's share of the call is not on the device's clock; max over "
-                             "ranks per step; mean, p50 and p90 over steps",
+                             "stream; before each timed call the ranks are released together by a "
+                             "device-side barrier over NVLink and a fixed device-side idle period is "
+                             "queued so the host's share of the call is not on the device's clock; max "
+                             "over ranks per step; mean, p50 and p90 over steps",
                    "combine": "zero_copy=True" if args.zero_copy else "zero_copy=False",
                    "recv_x": "in place (symmetric memory)" if (R > 1 or args.force_staged) else
                              "caller's tensor (single rank)"},

@@ -182,6 +182,17 @@ int mcep_buffer_set_option(mcep_buffer* buf, const char* name, int64_t value);
  * No counterpart in the reference, whose kernels trap instead. */
 int mcep_buffer_status(mcep_buffer* buf, int32_t* out, int n);
 
+/* A barrier of the group on the device, queued on `stream`: every rank writes
+ * one word into every active peer's symmetric memory and waits for theirs, so
+ * the ranks' streams leave it within about one NVLink latency of each other
+ * (a collective of a library completes at different times on different ranks).
+ * Every participating rank must call it the same number of times; ranks that
+ * `active_ranks` (device, [num_ranks], may be NULL) marks 0 are not waited for
+ * and must not call. The wait is bounded by "hard_timeout_ms" (status bit 2).
+ * The legacy Buffer of the reference has no barrier; its elastic buffer has one
+ * (mooncake-wheel/mooncake/mooncake_elastic_buffer.py:417-423). */
+int mcep_buffer_barrier(mcep_buffer* buf, const int32_t* active_ranks, uint64_t stream);
+
 /* Dispatch and combine calls this buffer has made (or adopted at a membership
  * refresh); in graph mode read from the device, after waiting for it to go
  * idle, so replayed graphs are counted. No counterpart in the reference. */

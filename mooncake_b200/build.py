@@ -12,8 +12,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 # MCEP_LIB points the package at a library built elsewhere (e.g. a diagnostic build)
 LIB = os.environ.get("MCEP_LIB") or os.path.join(HERE, "libmcep.so")
-SOURCES = ["ep_kernels.cu", "ep_runtime.cu", "ep_noalloc.cu"]
-HEADERS = ["ep_kernels.cuh", "ep_device.cuh", os.path.join("..", "..", "include", "mcep.h")]
+SOURCES = ["ep_kernels.cu", "ep_runtime.cu", "ep_noalloc.cu", "ep_elastic_kernels.cu",
+           "ep_elastic.cu"]
+HEADERS = ["ep_kernels.cuh", "ep_device.cuh", "ep_elastic.cuh", "ep_runtime_internal.h",
+           os.path.join("..", "..", "include", "mcep.h")]
 
 
 STAMP = LIB + ".sources"  # digest of the sources the library was built from

@@ -81,6 +81,24 @@ std::string drain_kernel_times() {
     return out;
 }
 
+LaunchScope::LaunchScope(const char* name, cudaStream_t stream) : name_(name), stream_(stream) {
+    if (g_timing.load()) {
+        cudaEventCreate(&a_);
+        cudaEventCreate(&b_);
+        cudaEventRecord(a_, stream_);
+    }
+}
+
+cudaError_t LaunchScope::done(cudaError_t err) {
+    if (a_ != nullptr) {
+        cudaEventRecord(b_, stream_);
+        std::lock_guard<std::mutex> lk(g_timing_mu);
+        g_recs.push_back(TimingRec{name_, a_, b_});
+    }
+    if (err == cudaSuccess) g_launches.fetch_add(1);
+    return err;
+}
+
 namespace kernels {
 
 constexpr unsigned kFull = 0xffffffffu;
@@ -1311,6 +1329,27 @@ __device__ __forceinline__ void resolve_seq(Params& p) {
 
 __global__ void ep_advance_seq_kernel(uint32_t* word) { *word += 2; }
 
+// One thread per rank: tell that rank "I am here", then wait until it has said
+// the same. Bounded: a rank that never comes raises the hard-timeout status bit
+// and the others go on.
+__global__ void __launch_bounds__(kMaxRanks) ep_barrier_kernel(BarrierParams p) {
+    const int r = threadIdx.x;
+    if (r >= p.R || r == p.rank) return;
+    if (p.active_ranks != nullptr && !ld_volatile_s32(p.active_ranks + r)) return;
+    char* peer = reinterpret_cast<char*>(p.peer_base[r]);
+    if (peer == nullptr) return;
+    st_release_sys(reinterpret_cast<uint64_t*>(peer + p.bar_off) + p.rank, (uint64_t)p.epoch);
+    const uint64_t* mine = reinterpret_cast<const uint64_t*>(p.local_base + p.bar_off) + r;
+    const uint64_t start = globaltimer_ns();
+    // (a peer that has left this barrier may already have announced the next one)
+    while ((int32_t)((uint32_t)ld_acquire_sys(mine) - p.epoch) < 0) {
+        if ((int64_t)(globaltimer_ns() - start) > p.hard_timeout_ns) {
+            atomicOr(p.status, kStatusHardTimeout);
+            return;
+        }
+    }
+}
+
 template <bool kFP8, bool kFused, int kPhases>
 __global__ void __launch_bounds__(512) ep_dispatch_kernel(GroupDispatchParams p) {
     extern __shared__ int smem_i32[];
@@ -1771,6 +1810,12 @@ cudaError_t launch_group_combine_reduce(const GroupCombineParams& p, const Launc
     auto k = ep_combine_kernel<2>;
     const int grid = persistent_grid(p.T, k, threads, 0, ctx);
     return launch("ep_combine_reduce", k, dim3(grid), dim3(threads), 0, ctx, p);
+}
+
+cudaError_t launch_barrier(const BarrierParams& p, const LaunchCtx& ctx) {
+    LaunchCtx plain = ctx;
+    plain.pdl = false;
+    return launch("ep_barrier", ep_barrier_kernel, dim3(1), dim3(kMaxRanks), 0, plain, p);
 }
 
 cudaError_t launch_advance_seq(uint32_t* word, const LaunchCtx& ctx) {

@@ -191,11 +191,39 @@ cudaError_t launch_group_dispatch_multi(const GroupDispatchParams* params, int n
 cudaError_t launch_group_combine_multi(const GroupCombineParams* params, int n,
                                        GroupCombineParams* dev_params, const LaunchCtx& ctx);
 
+// A barrier of the group on the device: every rank writes one word to every
+// active peer and waits for theirs; the ranks leave within about one NVLink
+// latency of each other. `bar_off` = [R] u64 words in symmetric memory,
+// `epoch` = the number of this barrier (all ranks count alike).
+struct BarrierParams {
+    void* const* peer_base;
+    char* local_base;
+    const int32_t* active_ranks;  // [R] or null (all active)
+    size_t bar_off;
+    int rank, R;
+    uint32_t epoch;
+    int64_t hard_timeout_ns;
+    int32_t* status;
+};
+cudaError_t launch_barrier(const BarrierParams& p, const LaunchCtx& ctx);
+
 // Graph mode: after the last kernel of a call, the word that holds the next
 // sequence number of that call's parity moves on by two.
 cudaError_t launch_advance_seq(uint32_t* word, const LaunchCtx& ctx);
 
 uint64_t kernel_launch_count();
+// Brackets a launch made outside ep_kernels.cu so that it is counted - and, when
+// per-kernel timing is on, timed - like the launches made there.
+class LaunchScope {
+public:
+    LaunchScope(const char* name, cudaStream_t stream);
+    cudaError_t done(cudaError_t err);  // pass cudaGetLastError() of the launch
+
+private:
+    const char* name_;
+    cudaStream_t stream_;
+    cudaEvent_t a_ = nullptr, b_ = nullptr;
+};
 // Per-kernel device times: switch on, run, then drain "name launches total_ms" lines.
 void set_kernel_timing(bool on);
 std::string drain_kernel_times();

@@ -18,6 +18,7 @@
 
 #include "../../include/mcep.h"
 #include "ep_kernels.cuh"
+#include "ep_runtime_internal.h"
 
 namespace {
 
@@ -61,7 +62,8 @@ constexpr size_t kWordBlock = (size_t)MCEP_MAX_EXPERTS * sizeof(uint64_t);
 constexpr size_t kHeaderParity = 128u << 10;
 constexpr size_t kHeaderRegion = 2 * kHeaderParity;
 constexpr size_t kPubSeqOff = kHeaderRegion - 256;
-static_assert(2 * kWordBlock + 2 * 64 * sizeof(uint64_t) <= kHeaderParity - 256, "header layout");
+constexpr size_t kBarrierOff = kHeaderParity - 1024;  // [64] u64 barrier words (free tail of parity 0's block)
+static_assert(2 * kWordBlock + 2 * 64 * sizeof(uint64_t) <= kHeaderParity - 1024, "header layout");
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -220,6 +222,7 @@ struct mcep_buffer {
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t ev_a = nullptr, ev_b = nullptr;  // reusable ordering events
     uint32_t dseq = 0, cseq = 0;     // dispatch / combine calls issued so far
+    uint32_t barrier_epoch = 0;      // barriers issued so far
 
     // workspace carve-up (per parity so two calls in flight do not share scratch)
     struct Scratch {
@@ -245,6 +248,7 @@ struct mcep_buffer {
         mcep::GroupDispatchParams d;
         mcep::GroupCombineParams c;
     } pending;
+    std::function<int()> after_deferred;  // run once the prepared dispatch has been launched
 
     // what combine needs to know about the dispatch call a handle came from
     struct DispatchRecord {
@@ -321,6 +325,29 @@ bool chain_with_pdl(const mcep_buffer* b, cudaStream_t stream) {
     return st == cudaStreamCaptureStatusNone;
 }
 }  // namespace
+
+namespace mcep {
+
+BufferView view_of(mcep_buffer* b) {
+    BufferView v;
+    v.base = b->base, v.data_off = kHeaderRegion, v.num_bytes = b->num_bytes;
+    v.peer_host = b->peer_host.data();
+    v.rank = b->rank, v.num_ranks = b->num_ranks, v.num_sms = b->num_sms;
+    v.status = b->status, v.comm_stream = b->comm_stream;
+    v.group = b->num_ranks > 1 || b->force_staged;
+    v.defer = b->defer;
+    return v;
+}
+
+size_t exchange_bytes(int num_ranks, int num_experts, int M, int hidden) {
+    return 2 * geometry(num_ranks, num_experts, M, hidden, false).parity_bytes;
+}
+
+void set_after_deferred(mcep_buffer* b, std::function<int()> fn) { b->after_deferred = std::move(fn); }
+
+int report_failure(int code, const char* message) { return fail(code, "%s", message); }
+
+}  // namespace mcep
 
 extern "C" {
 
@@ -457,6 +484,7 @@ int mcep_buffer_destroy(mcep_buffer* b) {
     cudaGetDevice(&cur);
     if (cur != b->device) cudaSetDevice(b->device);
     cudaDeviceSynchronize();
+    mcep::elastic_release(b);
     for (void* p : b->ipc_opened) cudaIpcCloseMemHandle(p);
     if (b->fabric) {
         for (auto& m : b->fabric_peers) fabric_unmap(driver_api(), &m);
@@ -510,7 +538,7 @@ static int write_device_seq(mcep_buffer* b) {
 
 static int publish_seq(mcep_buffer* b) {
     if (int rc = read_device_seq(b)) return rc;
-    const uint32_t pub[2] = {b->dseq, b->cseq};
+    const uint32_t pub[3] = {b->dseq, b->cseq, b->barrier_epoch};
     MCEP_CUDA(cudaMemcpy(b->base + kPubSeqOff, pub, sizeof(pub), cudaMemcpyHostToDevice));
     return MCEP_OK;
 }
@@ -519,11 +547,12 @@ static int adopt_largest_seq(mcep_buffer* b) {
     uint32_t d = b->dseq, c = b->cseq;
     for (int r = 0; r < b->num_ranks; ++r) {
         if (r == b->rank || !b->available[r] || b->peer_host[r] == nullptr) continue;
-        uint32_t pub[2] = {0, 0};
+        uint32_t pub[3] = {0, 0, 0};
         MCEP_CUDA(cudaMemcpy(pub, static_cast<char*>(b->peer_host[r]) + kPubSeqOff, sizeof(pub),
                              cudaMemcpyDeviceToHost));
         if (pub[0] > d) d = pub[0];
         if (pub[1] > c) c = pub[1];
+        if (pub[2] > b->barrier_epoch) b->barrier_epoch = pub[2];  // barriers are counted alike, too
     }
     if (d != b->dseq || c != b->cseq) {
         // handles of calls made before the jump no longer name a known call
@@ -1127,6 +1156,23 @@ int mcep_combine(mcep_buffer* b, const mcep_combine_args* a, mcep_event** out_ev
 }
 
 // -----------------------------------------------------------------------------
+// barrier
+// -----------------------------------------------------------------------------
+int mcep_buffer_barrier(mcep_buffer* b, const int32_t* active_ranks, uint64_t stream) {
+    MCEP_REQUIRE(b != nullptr);
+    if (b->num_ranks == 1) return MCEP_OK;
+    if (int rc = check_connected(b)) return rc;
+    mcep::BarrierParams p = {};
+    p.peer_base = b->peer_dev, p.local_base = b->base, p.active_ranks = active_ranks;
+    p.bar_off = kBarrierOff, p.rank = b->rank, p.R = b->num_ranks;
+    p.epoch = ++b->barrier_epoch;
+    p.hard_timeout_ns = b->hard_timeout_ns, p.status = b->status;
+    mcep::LaunchCtx ctx{reinterpret_cast<cudaStream_t>(stream), b->num_sms, false};
+    MCEP_CUDA(mcep::launch_barrier(p, ctx));
+    return MCEP_OK;
+}
+
+// -----------------------------------------------------------------------------
 // in-process groups: start what the ranks have prepared, in one launch
 // -----------------------------------------------------------------------------
 int mcep_launch_deferred(mcep_buffer* const* bufs, int n) {
@@ -1176,9 +1222,16 @@ int mcep_launch_deferred(mcep_buffer* const* bufs, int n) {
                                              static_cast<mcep::GroupCombineParams*>(dev_params), ctx);
     for (mcep_buffer* b : who) b->pending.kind = 0;
     MCEP_CUDA(e);
-    if (kind == 1)
+    if (kind == 1) {
         for (mcep_buffer* b : who)
             if (b->pending.then_second) MCEP_CUDA(mcep::launch_group_dispatch_recv(b->pending.d, ctx));
+        for (mcep_buffer* b : who) {
+            if (!b->after_deferred) continue;
+            std::function<int()> fn;
+            fn.swap(b->after_deferred);
+            if (int rc = fn()) return rc;
+        }
+    }
     return MCEP_OK;
 }
 

@@ -73,6 +73,7 @@ def _load() -> ctypes.CDLL:
         "mcep_buffer_set_peer_bases": (i32, [vp, _c.POINTER(vp), _c.POINTER(_c.c_int32)]),
         "mcep_buffer_set_option": (i32, [vp, _c.c_char_p, i64]),
         "mcep_buffer_status": (i32, [vp, _c.POINTER(_c.c_int32), i32]),
+        "mcep_buffer_barrier": (i32, [vp, vp, u64]),
         "mcep_buffer_call_counts": (i32, [vp, _c.POINTER(_c.c_uint32), _c.POINTER(_c.c_uint32)]),
         "mcep_buffer_next_recv_x": (i32, [vp, i32, i32, i32, i32, _c.POINTER(vp),
                                           _c.POINTER(_c.c_size_t)]),
@@ -267,6 +268,12 @@ class Buffer:
         out = (_c.c_int32 * 1)()
         _check(_lib.mcep_buffer_status(self._h, out, 1))
         return int(out[0])
+
+    def barrier(self, stream_ptr: int = 0, active_ranks_ptr: int = 0) -> None:
+        """Device-side barrier of the group on `stream_ptr` (include/mcep.h:
+        mcep_buffer_barrier): the ranks leave it within about a microsecond of
+        each other."""
+        _check(_lib.mcep_buffer_barrier(self._h, active_ranks_ptr or None, stream_ptr))
 
     def call_counts(self) -> Tuple[int, int]:
         """(dispatch calls, combine calls) made or adopted so far."""

@@ -47,6 +47,12 @@ def run_case(cfg, group, rank, R, buf_cache):
         dist.barrier()
     if not active[rank]:
         return  # an inactive rank makes no call
+    # the device-side barrier of the group (ranks marked inactive are not waited for)
+    ar_dev = torch.tensor(active, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        buf.runtime.barrier(torch.cuda.current_stream().cuda_stream, ar_dev.data_ptr())
+    torch.cuda.synchronize()
+    assert buf.runtime.status() == 0, "barrier timed out"
     buf.recv_in_place = cfg.get("recv_in_place", True)
     x, idx, w = xs[rank].cuda(), idxs[rank].cuda(), ws[rank].cuda()
     ar = torch.tensor(active, dtype=torch.int32, device="cuda")

@@ -167,3 +167,32 @@ def test_every_entry_point_cites_what_it_replaces():
         near = " ".join(comments[-3:])
         assert re.search(r"mooncake-[a-z-]+/|no counterpart|No counterpart|not in the reference|"
                          r"Measurement aid|last failure|has launched", near), name
+
+
+def test_library_is_rebuilt_when_its_sources_change(tmp_path, monkeypatch):
+    """The library is judged stale by the CONTENT of its sources (a digest kept
+    beside it), not by file times: a copy of the tree keeps no times, and a
+    library older than its sources must not be loaded in silence."""
+    from mooncake_b200 import build
+    assert not build._stale()
+    stamp = open(build.STAMP).read()
+    monkeypatch.setattr(build, "STAMP", str(tmp_path / "stamp"))
+    assert build._stale()                      # no record of what it was built from
+    (tmp_path / "stamp").write_text(stamp)
+    assert not build._stale()
+    (tmp_path / "stamp").write_text("0" * 64)  # built from something else
+    assert build._stale()
+    monkeypatch.setenv("MCEP_NVCC_FLAGS", "-DSOMETHING")
+    (tmp_path / "stamp").write_text(stamp)
+    assert build._stale()                      # other compiler flags are other sources
+
+
+def test_mooncake_checkout_is_found_through_the_environment(tmp_path, monkeypatch):
+    from oracle import build as ob
+    fake = tmp_path / "tree"
+    (fake / "mooncake-ep" / "src").mkdir(parents=True)
+    (fake / "mooncake-ep" / "src" / "mooncake_ep_kernel.cu").write_text("// stand-in")
+    monkeypatch.setenv("MOONCAKE_SRC", str(fake))
+    assert ob.find_mooncake_src() == str(fake)
+    monkeypatch.setenv("MOONCAKE_SRC", str(tmp_path / "nowhere"))
+    assert ob.find_mooncake_src() != str(tmp_path / "nowhere")
