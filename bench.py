@@ -458,6 +458,83 @@ def timed_steps(layer, n_steps, n_warm, flush, sync, hide_host):
             step)
 
 
+def elastic_block(w, layer, group, rank, R, dev, flush, sync, n_steps):
+    """The same inputs through the elastic-style interface (`ElasticBuffer`: a token
+    travels once per destination rank, flat receive rows, unweighted combine), bf16
+    payloads, timed like the headline. Returns this rank's per-step times."""
+    import torch
+    import torch.distributed as dist
+    from mooncake_b200.mooncake_elastic_buffer import ElasticBuffer
+    T, H, E, K = w["T"], w["H"], w["E"], w["K"]
+    buf = ElasticBuffer(group, num_max_tokens_per_rank=T, hidden=H, num_topk=K, num_gpu_timeout_secs=2)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def align():
+        if R > 1:
+            dist.all_reduce(sync)
+            buf.runtime.barrier(stream, 0)
+        # the wrapper allocates its outputs inside the call: a longer idle period hides that too
+        torch.cuda._sleep(3 * HOST_HIDE_CYCLES)
+
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_steps)]
+    rows = 0
+    for i in range(-3, n_steps):
+        ev = evs[i] if i >= 0 else None
+        if flush is not None:
+            flush.zero_()
+        align()
+        if ev:
+            ev[0].record()
+        recv, _, _, handle, _ = buf.dispatch(layer.x, topk_idx=layer.idx, topk_weights=layer.wts,
+                                             num_experts=E, num_max_tokens_per_rank=T, do_cpu_sync=False)
+        if ev:
+            ev[1].record()
+        if flush is not None:
+            flush.zero_()
+        align()
+        if ev:
+            ev[2].record()
+        out, _, _ = buf.combine(recv, handle)  # identity expert
+        if ev:
+            ev[3].record()
+        if i == -1:
+            torch.cuda.synchronize()
+            rows = int(handle.psum_num_recv_tokens_per_scaleup_rank[-1])
+            assert buf.runtime.status() == 0, "device-side anomaly in the elastic calls"
+    torch.cuda.synchronize()
+    td = [e[0].elapsed_time(e[1]) for e in evs]
+    tc = [e[2].elapsed_time(e[3]) for e in evs]
+    buf.destroy()
+    return td, tc, rows
+
+
+def elastic_nvlink_us(w, R, idx_all):
+    """Link time of the elastic exchange on the busiest GPU: one bf16 row per (token,
+    remote destination rank) each way, over 900 GB/s per direction."""
+    L = w["E"] // R
+    eg, ing = [0] * R, [0] * R
+    for s, idx in enumerate(idx_all):
+        ranks = torch_unique_ranks(idx, L, R)
+        for d in range(R):
+            if d != s:
+                n = int(ranks[:, d].sum())
+                eg[s] += n
+                ing[d] += n
+    rows = max(max(eg), max(ing))
+    return 2 * rows * 2 * w["H"] / 900e9 * 1e6, rows
+
+
+def torch_unique_ranks(idx, L, R):
+    """[T, R] bool: does token t name an expert of rank r."""
+    import torch
+    out = torch.zeros((idx.shape[0], R), dtype=torch.bool)
+    for k in range(idx.shape[1]):
+        col = idx[:, k]
+        ok = col >= 0
+        out[torch.nonzero(ok).squeeze(1), (col[ok] // L)] = True
+    return out
+
+
 def summarise(td, tc, dev, R):
     """Per-step max over ranks (the critical path), then mean / p50 / p90 over steps."""
     import torch
@@ -470,7 +547,8 @@ def summarise(td, tc, dev, R):
     layer_ms = td + tc
     q = lambda t, p: float(torch.quantile(t, p))  # noqa: E731
     return {"us_per_layer": float(layer_ms.mean()) * 1e3, "us_per_layer_p50": q(layer_ms, 0.5) * 1e3,
-            "us_per_layer_p90": q(layer_ms, 0.9) * 1e3, "dispatch_us": float(td.mean()) * 1e3,
+            "us_per_layer_p90": q(layer_ms, 0.9) * 1e3, "us_per_layer_max": float(layer_ms.max()) * 1e3,
+            "dispatch_us": float(td.mean()) * 1e3,
             "dispatch_us_p50": q(td, 0.5) * 1e3, "combine_us": float(tc.mean()) * 1e3,
             "combine_us_p50": q(tc, 0.5) * 1e3}
 
@@ -690,6 +768,22 @@ def run_ours(args):
                    "kernels": k3}
         del l3
 
+    # ---- the elastic-style interface on the same inputs ------------------------------------
+    elastic = None
+    if not args.no_extras and inactive < 0 and not args.force_staged and w["T"] <= 1024:
+        elayer = Layer(args, w, group, rank, R, dev, zero_copy=False) if prefill is not None else layer
+        tde, tce, rows = elastic_block(w, elayer, group, rank, R, dev, flush, sync_word, max(10, K_steps // 2))
+        ze = summarise(tde, tce, dev, R)
+        elastic = {"us_per_layer": ze["us_per_layer"], "us_per_layer_p50": ze["us_per_layer_p50"],
+                   "dispatch_us": ze["dispatch_us"], "combine_us": ze["combine_us"],
+                   "rows_received_rank0": rows, "payload": "bf16",
+                   "how": "ElasticBuffer.dispatch(do_cpu_sync=False) + ElasticBuffer.combine on the "
+                          "headline's inputs, identity expert, timed like the headline"}
+        if R > 1 and rank == 0:
+            us, nrows = elastic_nvlink_us(w, R, idx_all)
+            elastic.update({"nvlink_roofline_us": us, "rows_busiest_gpu": nrows,
+                            "nvlink_frac_of_peak": us / ze["us_per_layer"]})
+
     if rank != 0:
         if R > 1:
             dist.destroy_process_group()
@@ -731,7 +825,7 @@ def run_ours(args):
                 "how": "host wall clock around [H2D x, idx -> dispatch -> D2H recv_count] + "
                        "[H2D weights -> combine -> D2H combined_x], pinned host memory"},
         "roofline": roofline, "nvlink": nvlink, "zero_copy_combine": zero_copy,
-        "prefill_1gpu": prefill, "kernels": kern, "cpu_baseline": cpu_baseline,
+        "prefill_1gpu": prefill, "elastic": elastic, "kernels": kern, "cpu_baseline": cpu_baseline,
     }
     print(json.dumps(line), flush=True)
     if R > 1:

@@ -305,6 +305,102 @@ typedef struct mcep_combine_args {
 int mcep_combine(mcep_buffer* buf, const mcep_combine_args* args,
                  mcep_event** out_event, mcep_hook** out_hook);
 
+/* ---- elastic-style calls -----------------------------------------------------
+ * The interface of the reference's ElasticBuffer for one NVLink domain
+ * (mooncake-wheel/mooncake/mooncake_elastic_buffer.py:437-774; host side
+ * mooncake-ep/src/mooncake_ep_elastic_buffer.cpp:230-426; device side
+ * mooncake-ep/include/elastic/mooncake_ep_elastic_dispatch_official.cuh,
+ * ..._dispatch_copy_epilogue.cuh, ..._combine_official.cuh,
+ * ..._combine_reduce_epilogue.cuh), on the exchange of mcep_dispatch /
+ * mcep_combine with every rank standing for one "expert":
+ *   - a token travels ONCE to every rank that owns at least one of its experts
+ *     (the reference deduplicates the same way, dispatch_official.cuh:113-117);
+ *   - the receiver gets the rows flat, ordered by source rank, then by token
+ *     index (the order of the reference's `deterministic` mode);
+ *   - combine sends ONE row per received token back and the token's owner adds
+ *     the rows of the ranks it reached, in the order of each rank's last listing
+ *     in the token's top-k list, unweighted.
+ * Outputs of dispatch (caller-allocated, capacities as the reference allocates
+ * them: n_cap = num_ranks * num_max_tokens_per_rank rows, times num_topk for
+ * recv_x / recv_topk_weights when do_expand):
+ *   psum_num_recv_tokens_per_scaleup_rank [R] int32  inclusive sum of the rows each source sent
+ *   psum_num_recv_tokens_per_expert [L+1] int32  exclusive sum of the per-expert
+ *       (token, expert) hits, each rounded up to expert_alignment; with
+ *       do_expand entries < L end up as the END of each expert's segment, as the
+ *       reference's epilogue leaves them (dispatch_copy_epilogue.cuh:138-141)
+ *   dst_buffer_slot_idx [T][K] int32  rank * M + position of the token among this
+ *       rank's tokens for that destination, at the lane that sends; else -1
+ *   recv_x [n][H] bf16; with do_expand one row per (received token, local expert
+ *       it chose), experts' segments in order, rows of an expert in receive order
+ *   recv_topk_idx [n][K] int64  local expert index or -1
+ *   recv_topk_weights [n][K] fp32 (do_expand: [rows], the weight of that choice); optional
+ *   recv_src_metadata [n][K+2] int32: source rank * M + token, source rank * K +
+ *       last lane that names a local expert, and with do_expand the row of each lane
+ * Rows beyond the received count are left untouched. Only bf16 payloads
+ * (x_element_size 2, no scale packs); the reference's pre-quantised (x, sf)
+ * input is not built. `cached_mode` (dispatch again with the routing of an
+ * earlier handle) recomputes the same layout from `topk_idx` - pass the
+ * handle's copy of it. */
+typedef struct mcep_elastic_dispatch_args {
+    const void* x;               /* [num_tokens][hidden] */
+    int32_t x_element_size;      /* 2 */
+    const void* sf;              /* must be NULL */
+    int32_t num_tokens, hidden, num_sf_packs, sf_token_stride, sf_hidden_stride;
+    const int64_t* topk_idx;     /* [num_tokens][num_topk] */
+    int32_t num_topk;
+    const float* topk_weights;   /* [num_tokens][num_topk] or NULL */
+    int32_t* active_ranks;       /* [num_ranks], as in mcep_dispatch */
+    int32_t num_experts, num_max_tokens_per_rank, expert_alignment;
+    int32_t do_expand, cached_mode;
+    int64_t timeout_us;          /* the reference's num_gpu_timeout_secs, in microseconds; -1: hard bound only */
+    int32_t async_with_compute_stream;  /* run on the communication stream, return an event */
+    uint64_t compute_stream;
+    int32_t* psum_num_recv_tokens_per_scaleup_rank;
+    int32_t* psum_num_recv_tokens_per_expert;
+    int32_t* dst_buffer_slot_idx;
+    void* recv_x;
+    void* recv_x_scales;         /* must be NULL */
+    int64_t* recv_topk_idx;
+    float* recv_topk_weights;    /* or NULL */
+    int32_t* recv_src_metadata;
+} mcep_elastic_dispatch_args;
+int mcep_elastic_dispatch(mcep_buffer* buf, const mcep_elastic_dispatch_args* args,
+                          mcep_event** out_event);
+
+/* Replaces MooncakeElasticBuffer::combine
+ * (mooncake-ep/src/mooncake_ep_elastic_buffer.cpp:362-426).
+ * x: [n][H] bf16, one row per received token (do_expand: the expanded rows,
+ * summed per received token before they travel - one row copied, two added as
+ * one bf16 addition, more accumulated in fp32 and rounded once:
+ * mooncake-ep/include/elastic/mooncake_ep_elastic_combine_official.cuh:146-216
+ * with multiple reduction). `recv_src_metadata`
+ * must be the tensor a dispatch call of this buffer filled, one of its last
+ * two; `topk_idx` the [T][K] tensor of that call. `topk_weights` is accepted
+ * and not used by the reduction, as in the reference's forward pass. */
+typedef struct mcep_elastic_combine_args {
+    const void* x;
+    int32_t num_input_tokens, hidden;
+    const int64_t* topk_idx;
+    int32_t num_combined_tokens, num_topk;
+    const float* topk_weights;
+    const int32_t* psum_num_recv_tokens_per_scaleup_rank;
+    const int32_t* recv_src_metadata;
+    int32_t* active_ranks;
+    int32_t num_experts, num_max_tokens_per_rank, do_expand;
+    int64_t timeout_us;
+    int32_t async_with_compute_stream;
+    uint64_t compute_stream;
+    void* combined_x;            /* [num_combined_tokens][hidden] bf16 */
+} mcep_elastic_combine_args;
+int mcep_elastic_combine(mcep_buffer* buf, const mcep_elastic_combine_args* args,
+                         mcep_event** out_event);
+
+/* Bytes an mcep_buffer needs for the elastic calls of this shape (the counterpart
+ * of ElasticBuffer.get_buffer_size_hint,
+ * mooncake-wheel/mooncake/mooncake_elastic_buffer.py:315-358). */
+uint64_t mcep_elastic_buffer_size_hint(int num_max_tokens_per_rank, int hidden,
+                                       int num_ranks, int num_topk);
+
 /* ---- events and hooks --------------------------------------------------------
  * mooncake-ep/include/mooncake_ep_event.h:9-44 (EventHandle) and the
  * std::function returned by dispatch/combine. */

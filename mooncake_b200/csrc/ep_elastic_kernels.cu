@@ -270,28 +270,33 @@ __global__ void __launch_bounds__(kThreads) ep_elastic_local_reduce_kernel(Elast
                 st32(dst + c, ld32_readonly(static_cast<const char*>(p.x) + (size_t)s * row_bytes + c));
             continue;
         }
+        // the rows to add, in listing order (gathered before the lanes' loops part ways)
+        int rows[kMaxTopk];
+        {
+            unsigned todo = valid;
+#pragma unroll
+            for (int j = 0; j < kMaxTopk; ++j) {
+                const int k = todo ? __ffs(todo) - 1 : 0;
+                const int s = __shfl_sync(kAll, slot, k);
+                rows[j] = todo ? s : -1;
+                todo &= todo - 1;
+            }
+        }
         for (int c = lane * 32; c < row_bytes; c += 32 * 32) {
             float acc[16];
-            unsigned todo = valid;
-            bool first = cnt == 2;  // two rows: a + b, not 0 + a + b (the sign of a zero sum differs)
 #pragma unroll
             for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-            while (todo) {
-                const int k = __ffs(todo) - 1;
-                todo &= todo - 1;
-                const int s = __shfl_sync(kAll, slot, k);
-                const V32 v = ld32_readonly(static_cast<const char*>(p.x) + (size_t)s * row_bytes + c);
+#pragma unroll
+            for (int m = 0; m < kMaxTopk; ++m) {
+                if (m >= cnt) break;
+                const V32 v = ld32_readonly(static_cast<const char*>(p.x) + (size_t)rows[m] * row_bytes + c);
+                // two rows: a + b, not 0 + a + b (the sign of a zero sum differs)
+                const bool first = m == 0 && cnt == 2;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    if (first) {
-                        acc[2 * j] = bf16lo(v.w[j]);
-                        acc[2 * j + 1] = bf16hi(v.w[j]);
-                    } else {
-                        acc[2 * j] = __fadd_rn(acc[2 * j], bf16lo(v.w[j]));
-                        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], bf16hi(v.w[j]));
-                    }
+                    acc[2 * j] = first ? bf16lo(v.w[j]) : __fadd_rn(acc[2 * j], bf16lo(v.w[j]));
+                    acc[2 * j + 1] = first ? bf16hi(v.w[j]) : __fadd_rn(acc[2 * j + 1], bf16hi(v.w[j]));
                 }
-                first = false;
             }
             st32(dst + c, pack_bf16x16(acc));
         }

@@ -47,6 +47,37 @@ class _CombineArgs(_c.Structure):
     ]
 
 
+class _ElasticDispatchArgs(_c.Structure):
+    _fields_ = [
+        ("x", _c.c_void_p), ("x_element_size", _c.c_int32), ("sf", _c.c_void_p),
+        ("num_tokens", _c.c_int32), ("hidden", _c.c_int32), ("num_sf_packs", _c.c_int32),
+        ("sf_token_stride", _c.c_int32), ("sf_hidden_stride", _c.c_int32),
+        ("topk_idx", _c.c_void_p), ("num_topk", _c.c_int32), ("topk_weights", _c.c_void_p),
+        ("active_ranks", _c.c_void_p),
+        ("num_experts", _c.c_int32), ("num_max_tokens_per_rank", _c.c_int32),
+        ("expert_alignment", _c.c_int32), ("do_expand", _c.c_int32), ("cached_mode", _c.c_int32),
+        ("timeout_us", _c.c_int64), ("async_with_compute_stream", _c.c_int32),
+        ("compute_stream", _c.c_uint64),
+        ("psum_num_recv_tokens_per_scaleup_rank", _c.c_void_p),
+        ("psum_num_recv_tokens_per_expert", _c.c_void_p), ("dst_buffer_slot_idx", _c.c_void_p),
+        ("recv_x", _c.c_void_p), ("recv_x_scales", _c.c_void_p), ("recv_topk_idx", _c.c_void_p),
+        ("recv_topk_weights", _c.c_void_p), ("recv_src_metadata", _c.c_void_p),
+    ]
+
+
+class _ElasticCombineArgs(_c.Structure):
+    _fields_ = [
+        ("x", _c.c_void_p), ("num_input_tokens", _c.c_int32), ("hidden", _c.c_int32),
+        ("topk_idx", _c.c_void_p), ("num_combined_tokens", _c.c_int32), ("num_topk", _c.c_int32),
+        ("topk_weights", _c.c_void_p), ("psum_num_recv_tokens_per_scaleup_rank", _c.c_void_p),
+        ("recv_src_metadata", _c.c_void_p), ("active_ranks", _c.c_void_p),
+        ("num_experts", _c.c_int32), ("num_max_tokens_per_rank", _c.c_int32),
+        ("do_expand", _c.c_int32), ("timeout_us", _c.c_int64),
+        ("async_with_compute_stream", _c.c_int32), ("compute_stream", _c.c_uint64),
+        ("combined_x", _c.c_void_p),
+    ]
+
+
 def _load() -> ctypes.CDLL:
     # builds the library when it is missing or older than its sources (where the
     # sources and a compiler are present; a prebuilt library alone is taken as is)
@@ -82,6 +113,9 @@ def _load() -> ctypes.CDLL:
         "mcep_launch_deferred": (i32, [_c.POINTER(vp), i32]),
         "mcep_dispatch": (i32, [vp, _c.POINTER(_DispatchArgs), _c.POINTER(vp), _c.POINTER(vp)]),
         "mcep_combine": (i32, [vp, _c.POINTER(_CombineArgs), _c.POINTER(vp), _c.POINTER(vp)]),
+        "mcep_elastic_dispatch": (i32, [vp, _c.POINTER(_ElasticDispatchArgs), _c.POINTER(vp)]),
+        "mcep_elastic_combine": (i32, [vp, _c.POINTER(_ElasticCombineArgs), _c.POINTER(vp)]),
+        "mcep_elastic_buffer_size_hint": (u64, [i32, i32, i32, i32]),
         "mcep_event_create": (i32, [u64, _c.POINTER(vp)]),
         "mcep_event_current_stream_wait": (i32, [vp, u64]),
         "mcep_event_synchronize": (i32, [vp]),
@@ -344,6 +378,64 @@ class Buffer:
         _check(_lib.mcep_combine(self._h, _c.byref(a), _c.byref(ev), _c.byref(hk)))
         return (EventHandle(_adopt=ev.value) if ev.value else None,
                 _Hook(hk.value) if hk.value else None)
+
+
+    # -- elastic-style calls (mooncake-ep/src/mooncake_ep_elastic_buffer.cpp:230-426) -----
+    def elastic_dispatch(self, x_ptr: int, x_element_size: int, sf_ptr: int, num_tokens: int,
+                         hidden: int, num_sf_packs: int, sf_token_stride: int,
+                         sf_hidden_stride: int, topk_idx_ptr: int, num_topk: int,
+                         topk_weights_ptr: int, active_ranks_ptr: int, num_experts: int,
+                         num_max_tokens_per_rank: int, expert_alignment: int, do_expand: bool,
+                         async_with_compute_stream: bool, compute_stream_ptr: int,
+                         cached_mode: bool, psum_rank_ptr: int, psum_expert_ptr: int,
+                         dst_buffer_slot_idx_ptr: int, recv_x_ptr: int, recv_x_scales_ptr: int,
+                         recv_topk_idx_ptr: int, recv_topk_weights_ptr: int,
+                         recv_src_metadata_ptr: int, timeout_us: int = -1
+                         ) -> Optional[EventHandle]:
+        a = _ElasticDispatchArgs()
+        a.x, a.x_element_size, a.sf = x_ptr, x_element_size, sf_ptr or None
+        a.num_tokens, a.hidden, a.num_sf_packs = num_tokens, hidden, num_sf_packs
+        a.sf_token_stride, a.sf_hidden_stride = sf_token_stride, sf_hidden_stride
+        a.topk_idx, a.num_topk, a.topk_weights = topk_idx_ptr, num_topk, topk_weights_ptr or None
+        a.active_ranks = active_ranks_ptr
+        a.num_experts, a.num_max_tokens_per_rank = num_experts, num_max_tokens_per_rank
+        a.expert_alignment, a.do_expand, a.cached_mode = expert_alignment, int(do_expand), int(cached_mode)
+        a.timeout_us = timeout_us
+        a.async_with_compute_stream, a.compute_stream = int(async_with_compute_stream), compute_stream_ptr
+        a.psum_num_recv_tokens_per_scaleup_rank = psum_rank_ptr
+        a.psum_num_recv_tokens_per_expert = psum_expert_ptr
+        a.dst_buffer_slot_idx = dst_buffer_slot_idx_ptr
+        a.recv_x, a.recv_x_scales = recv_x_ptr, recv_x_scales_ptr or None
+        a.recv_topk_idx, a.recv_topk_weights = recv_topk_idx_ptr, recv_topk_weights_ptr or None
+        a.recv_src_metadata = recv_src_metadata_ptr
+        ev = _c.c_void_p()
+        _check(_lib.mcep_elastic_dispatch(self._h, _c.byref(a), _c.byref(ev)))
+        return EventHandle(_adopt=ev.value) if ev.value else None
+
+    def elastic_combine(self, x_ptr: int, num_input_tokens: int, hidden: int, topk_idx_ptr: int,
+                        num_combined_tokens: int, num_topk: int, topk_weights_ptr: int,
+                        psum_rank_ptr: int, recv_src_metadata_ptr: int, active_ranks_ptr: int,
+                        num_experts: int, num_max_tokens_per_rank: int, do_expand: bool,
+                        async_with_compute_stream: bool, compute_stream_ptr: int,
+                        combined_x_ptr: int, timeout_us: int = -1) -> Optional[EventHandle]:
+        a = _ElasticCombineArgs()
+        a.x, a.num_input_tokens, a.hidden = x_ptr or None, num_input_tokens, hidden
+        a.topk_idx, a.num_combined_tokens, a.num_topk = topk_idx_ptr, num_combined_tokens, num_topk
+        a.topk_weights = topk_weights_ptr or None
+        a.psum_num_recv_tokens_per_scaleup_rank = psum_rank_ptr
+        a.recv_src_metadata, a.active_ranks = recv_src_metadata_ptr, active_ranks_ptr
+        a.num_experts, a.num_max_tokens_per_rank = num_experts, num_max_tokens_per_rank
+        a.do_expand, a.timeout_us = int(do_expand), timeout_us
+        a.async_with_compute_stream, a.compute_stream = int(async_with_compute_stream), compute_stream_ptr
+        a.combined_x = combined_x_ptr or None
+        ev = _c.c_void_p()
+        _check(_lib.mcep_elastic_combine(self._h, _c.byref(a), _c.byref(ev)))
+        return EventHandle(_adopt=ev.value) if ev.value else None
+
+
+def elastic_buffer_size_hint(num_max_tokens_per_rank: int, hidden: int, num_ranks: int,
+                             num_topk: int) -> int:
+    return int(_lib.mcep_elastic_buffer_size_hint(num_max_tokens_per_rank, hidden, num_ranks, num_topk))
 
 
 def launch_deferred(buffers: List["Buffer"]) -> None:

@@ -199,6 +199,119 @@ def run_full_size_case(cfg, buf, rank, R, xs, idxs, ws, x, idx, w, ar):
     assert buf.runtime.status() == 0, "device status word set"
 
 
+def run_elastic_case(cfg, group, rank, R):
+    """`ElasticBuffer` as a model would use it, in the order of the reference's own
+    test (mooncake-ep/tests/test_elastic_buffer.py:229-392): a dispatch with CPU
+    sync and its combine, a dispatch with the cached handle, an asynchronous one
+    without CPU sync, an expanded one - each compared with the CPU oracle."""
+    from mooncake_b200.mooncake_elastic_buffer import ElasticBuffer
+    from oracle import elastic_oracle as eo
+    from tests.test_elastic_oracle import make_input, route_plan
+    M, E, H, K, T = cfg["M"], cfg["E"], cfg["H"], cfg["K"], cfg["T"]
+    align = cfg.get("alignment", 1)
+    if cfg.get("plan"):
+        plans = [route_plan(cfg["plan"], r, R, T, K, E) for r in range(R)]
+        idxs = [p[0] for p in plans]
+        xs = [make_input(r, T, H, 1_000_000) for r in range(R)]
+        ws = [torch.ones((T, K)) for _ in range(R)]
+    else:
+        plans = None
+        ins = [make_rank_inputs(cfg.get("seed", 1), r, T, H, E, K, cfg.get("routing", "uniform"), 4)
+               for r in range(R)]
+        xs, idxs, ws = [i[0] for i in ins], [i[1] for i in ins], [i[2] for i in ins]
+    buf = ElasticBuffer(group, num_max_tokens_per_rank=M, hidden=H, num_topk=K, num_gpu_timeout_secs=10)
+    x, idx, w = xs[rank].cuda(), idxs[rank].cuda(), ws[rank].cuda()
+    eq = lambda a, b: torch.equal(a.cpu().view(torch.int16), b.view(torch.int16))  # noqa: E731
+
+    def check_flat(recv, ridx, rw, handle, want, n, weights=True):
+        assert int(handle.psum_num_recv_tokens_per_scaleup_rank[-1]) == want["n"] == n
+        assert handle.psum_num_recv_tokens_per_scaleup_rank.cpu().tolist() == want["psum_rank"].tolist()
+        assert eq(recv[:n], want["recv_x"])
+        assert torch.equal(ridx[:n].cpu(), want["recv_topk_idx"])
+        assert torch.equal(handle.recv_src_metadata[:n, :2].cpu(), want["recv_src_metadata"][:, :2])
+        assert torch.equal(handle.dst_buffer_slot_idx.cpu(), want["dst_buffer_slot_idx"])
+        if weights:
+            assert torch.equal(rw[:n].cpu(), want["recv_topk_weights"])
+
+    # 1. CPU-sync dispatch: exact extents, per-expert counts on the host
+    want = eo.elastic_dispatch(xs, idxs, ws, E, M, align)
+    recv0, idx0, w0, h0, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E,
+                                          num_max_tokens_per_rank=M, expert_alignment=align,
+                                          do_cpu_sync=True)
+    torch.cuda.synchronize()
+    n0 = want[rank]["n"]
+    assert recv0.shape[0] == n0 and idx0.shape[0] == n0
+    check_flat(recv0, idx0, w0, h0, want[rank], n0)
+    assert h0.num_recv_tokens_per_expert_list == [(c + align - 1) // align * align
+                                                   for c in want[rank]["hits"]]
+    assert h0.psum_num_recv_tokens_per_expert.cpu().tolist() == want[rank]["psum_expert"].tolist()[1:]
+    if plans:
+        assert n0 == plans[rank][1]
+    y0 = (recv0.float() * (1.0 + rank / 8.0)).to(torch.bfloat16)
+    ys = [(want[r]["recv_x"].float() * (1.0 + r / 8.0)).to(torch.bfloat16) for r in range(R)]
+    comb0, _, _ = buf.combine(y0.contiguous(), h0, topk_weights=w0.contiguous())
+    torch.cuda.synchronize()
+    ref = eo.elastic_combine(ys, want, idxs, E)
+    assert eq(comb0, ref[rank])
+
+    # 2. the cached handle, new data, no routing inputs
+    xs1 = [(v.float() * 0.5 + 17).to(torch.bfloat16) for v in xs]
+    want1 = eo.elastic_dispatch(xs1, idxs, None, E, M, align)
+    recv1, idx1, _, h1, _ = buf.dispatch(xs1[rank].cuda(), handle=h0, num_experts=E, num_max_tokens_per_rank=M)
+    torch.cuda.synchronize()
+    check_flat(recv1, idx1, None, h1, want1[rank], n0, weights=False)
+    assert torch.equal(idx1[:n0], idx0[:n0])
+    comb1, _, _ = buf.combine(recv1[:max(n0, 1)].contiguous(), h1)
+    torch.cuda.synchronize()
+    ref1 = eo.elastic_combine([o["recv_x"] for o in want1], want1, idxs, E)
+    assert eq(comb1, ref1[rank])
+    if plans:
+        torch.testing.assert_close(comb1.cpu(), (xs1[rank].float() * plans[rank][2]).to(torch.bfloat16),
+                                   rtol=5e-2, atol=1e-3)
+
+    # 3. asynchronous, no CPU sync: outputs keep their capacity, the count is on the device
+    recv2, idx2, w2, h2, ev2 = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E,
+                                            num_max_tokens_per_rank=M, expert_alignment=align,
+                                            do_cpu_sync=False, async_with_compute_stream=True)
+    ev2.current_stream_wait()
+    torch.cuda.synchronize()
+    assert recv2.shape[0] == R * M and not h2.num_recv_tokens_per_expert_list
+    check_flat(recv2, idx2, w2, h2, want[rank], n0)
+    y2 = (recv2.float() * (1.0 + rank / 8.0)).to(torch.bfloat16)
+    comb2, _, ev3 = buf.combine(y2, h2, async_with_compute_stream=True)
+    ev3.current_stream_wait()
+    torch.cuda.synchronize()
+    assert eq(comb2, ref[rank])
+
+    # 4. expanded layout
+    wantx = eo.elastic_dispatch(xs, idxs, ws, E, M, align, do_expand=True)
+    rx, ix, wx, hx, _ = buf.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E,
+                                     num_max_tokens_per_rank=M, expert_alignment=align, do_expand=True,
+                                     do_cpu_sync=True)
+    torch.cuda.synchronize()
+    o = wantx[rank]
+    assert int(hx.psum_num_recv_tokens_per_scaleup_rank[-1]) == o["n"]
+    assert hx.psum_num_recv_tokens_per_expert.cpu().tolist() == o["psum_expert"].tolist()
+    assert rx.shape[0] == o["n_expanded"] == wx.shape[0] and ix.shape[0] == o["n"]
+    assert hx.num_recv_tokens_per_expert_list == o["hits"]
+    used = o["used"][:rx.shape[0]]
+    assert torch.equal(rx.cpu()[used].view(torch.int16), o["recv_x"][:rx.shape[0]][used].view(torch.int16))
+    assert torch.equal(wx.cpu()[used], o["recv_topk_weights"][:rx.shape[0]][used])
+    assert torch.equal(hx.recv_src_metadata.cpu(), o["recv_src_metadata"])
+    yx_all = [(wantx[r]["recv_x"].float() * (1.0 + r / 8.0)).to(torch.bfloat16) for r in range(R)]
+    yx = (rx.float() * (1.0 + rank / 8.0)).to(torch.bfloat16)
+    if yx.shape[0] == 0:
+        yx = torch.zeros((1, H), dtype=torch.bfloat16, device="cuda")
+    combx, _, _ = buf.combine(yx.contiguous(), hx)
+    torch.cuda.synchronize()
+    refx = eo.elastic_combine(yx_all, wantx, idxs, E, do_expand=True)
+    assert eq(combx, refx[rank])
+    assert buf.runtime.status() == 0
+    buf.barrier(with_cpu_sync=True)
+    assert buf.runtime.status() == 0
+    buf.destroy()
+
+
 def main():
     cases = json.loads(os.environ["MCEP_TEST_CASES"])
     rank, R = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -208,7 +321,10 @@ def main():
     cache = {}
     for name, cfg in cases.items():
         try:
-            run_case(cfg, group, rank, R, cache)
+            if cfg.get("elastic"):
+                run_elastic_case(cfg, group, rank, R)
+            else:
+                run_case(cfg, group, rank, R, cache)
         except AssertionError as exc:
             print(f"[rank {rank}] case {name} FAILED: {exc}", flush=True)
             raise

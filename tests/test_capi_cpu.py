@@ -122,15 +122,18 @@ def _header_struct(name):
     body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), text, flags=re.S).group(1)
     out = []
     for decl in [d.strip() for d in body.split(";") if d.strip()]:
-        m = re.match(r"(const\s+)?(\w+)\s*(\*?)\s*(\w+)$", decl)
+        m = re.match(r"(const\s+)?(\w+)\s*(\*?)\s*(\w+(?:\s*,\s*\w+)*)$", decl)
         assert m, decl
-        ctype, ptr, field = m.group(2), m.group(3), m.group(4)
-        out.append((field, 8 if ptr else _C_KINDS[ctype][1]))
+        ctype, ptr = m.group(2), m.group(3)
+        for field in [f.strip() for f in m.group(4).split(",")]:
+            out.append((field, 8 if ptr else _C_KINDS[ctype][1]))
     return out
 
 
 @pytest.mark.parametrize("cname,pyname", [("mcep_dispatch_args", "_DispatchArgs"),
-                                          ("mcep_combine_args", "_CombineArgs")])
+                                          ("mcep_combine_args", "_CombineArgs"),
+                                          ("mcep_elastic_dispatch_args", "_ElasticDispatchArgs"),
+                                          ("mcep_elastic_combine_args", "_ElasticCombineArgs")])
 def test_argument_structs_match_the_header(cname, pyname, tmp_path):
     """The ctypes mirror has the header's fields in the header's order, and the
     offsets a C compiler gives them."""
@@ -196,3 +199,47 @@ def test_mooncake_checkout_is_found_through_the_environment(tmp_path, monkeypatc
     assert ob.find_mooncake_src() == str(fake)
     monkeypatch.setenv("MOONCAKE_SRC", str(tmp_path / "nowhere"))
     assert ob.find_mooncake_src() != str(tmp_path / "nowhere")
+
+
+def test_elastic_wrapper_surface_and_loud_failure_without_a_gpu():
+    """The elastic wrapper has the reference's names (mooncake-wheel/mooncake/
+    mooncake_elastic_buffer.py:84-774), rejects what is not built before touching
+    the device, and has no CPU path."""
+    import inspect
+    import torch
+    from mooncake_b200.mooncake_elastic_buffer import ElasticBuffer, EPHandle
+
+    class Solo:
+        def rank(self):
+            return 0
+
+        def size(self):
+            return 1
+
+    sig = inspect.signature(ElasticBuffer.__init__)
+    for name in ("group", "num_bytes", "num_max_tokens_per_rank", "hidden", "num_topk", "use_fp8_dispatch",
+                 "deterministic", "allow_hybrid_mode", "allow_multiple_reduction", "num_gpu_timeout_secs"):
+        assert name in sig.parameters, name
+    for name in ("x", "topk_idx", "topk_weights", "num_experts", "num_max_tokens_per_rank", "expert_alignment",
+                 "handle", "do_expand", "do_cpu_sync", "num_sms", "async_with_compute_stream"):
+        assert name in inspect.signature(ElasticBuffer.dispatch).parameters, name
+    for name in ("x", "handle", "topk_weights", "num_sms", "async_with_compute_stream"):
+        assert name in inspect.signature(ElasticBuffer.combine).parameters, name
+    for name in ("update_ep_member", "destroy", "barrier", "get_buffer_size_hint", "get_theoretical_num_sms",
+                 "get_physical_domain_size", "get_logical_domain_size"):
+        assert hasattr(ElasticBuffer, name), name
+    md = torch.zeros((5, 6), dtype=torch.int32)
+    h = EPHandle(False, 8, 1, 16, 4, torch.zeros((3, 4), dtype=torch.int64), [], torch.zeros(1), torch.zeros(8),
+                 md, torch.zeros((3, 4)))
+    assert h.num_recv_tokens == 5 and h.native_handle is None
+    with pytest.raises(NotImplementedError):
+        ElasticBuffer(Solo(), use_fp8_dispatch=True)
+    with pytest.raises(NotImplementedError):
+        ElasticBuffer(Solo(), allow_multiple_reduction=False)
+    assert ElasticBuffer.get_buffer_size_hint(Solo(), 128, 4096, 8) == 0
+    from mooncake_b200 import ep
+    # 2 parities x R*M rows x (32 + 4H) bytes, plus the per-token records
+    assert ep.elastic_buffer_size_hint(128, 4096, 8, 8) == 2 * 8 * 128 * (32 + 4 * 4096) + 2 * 128 * 64
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="Failed: CUDA error"):
+            ElasticBuffer(Solo(), num_max_tokens_per_rank=16, hidden=256, num_topk=2)

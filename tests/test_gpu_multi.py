@@ -41,6 +41,12 @@ def _cases(R):
         "mixtral_t4096": dict(T=4096, M=4096, H=4096, E=8, K=2, fp8=False, check="properties"),
         "prefill_t4096": dict(T=4096, M=4096, H=7168, E=256, K=8, fp8=False, check="properties"),
     }
+    # the elastic-style interface (ElasticBuffer): the route plan of the reference's own test, and
+    # random routing with masked entries and an expert alignment
+    c["elastic_alltoall_plan"] = dict(elastic=True, plan="alltoall", T=32, M=128, H=4096, E=256, K=8)
+    c["elastic_uniform_aligned"] = dict(elastic=True, T=100, M=128, H=2048, E=8 * R, K=8, alignment=4,
+                                        seed=11)
+    c["elastic_t600"] = dict(elastic=True, T=600, M=1024, H=1024, E=4 * R, K=4, seed=12)
     if R >= 2:
         # the last rank is marked inactive on every rank and makes no call for three
         # layers; after a membership refresh it is back in step
