@@ -504,8 +504,24 @@ def elastic_block(w, layer, group, rank, R, dev, flush, sync, n_steps):
     torch.cuda.synchronize()
     td = [e[0].elapsed_time(e[1]) for e in evs]
     tc = [e[2].elapsed_time(e[3]) for e in evs]
+    # per-kernel device times of the same calls (events around every launch)
+    from mooncake_b200 import ep
+    ep.set_kernel_timing(True)
+    n_k = 10
+    for _ in range(n_k):
+        align()
+        recv, _, _, handle, _ = buf.dispatch(layer.x, topk_idx=layer.idx, topk_weights=layer.wts,
+                                             num_experts=E, num_max_tokens_per_rank=T, do_cpu_sync=False)
+        align()
+        buf.combine(recv, handle)
+    if R > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    kt = {k: round(ms * 1e3 / max(n, 1), 2) for k, (n, ms) in ep.drain_kernel_times().items()
+          if k != "ep_barrier"}
+    ep.set_kernel_timing(False)
     buf.destroy()
-    return td, tc, rows
+    return td, tc, rows, kt
 
 
 def elastic_nvlink_us(w, R, idx_all):
@@ -772,11 +788,12 @@ def run_ours(args):
     elastic = None
     if not args.no_extras and inactive < 0 and not args.force_staged and w["T"] <= 1024:
         elayer = Layer(args, w, group, rank, R, dev, zero_copy=False) if prefill is not None else layer
-        tde, tce, rows = elastic_block(w, elayer, group, rank, R, dev, flush, sync_word, max(10, K_steps // 2))
+        tde, tce, rows, ekt = elastic_block(w, elayer, group, rank, R, dev, flush, sync_word,
+                                            max(10, K_steps // 2))
         ze = summarise(tde, tce, dev, R)
         elastic = {"us_per_layer": ze["us_per_layer"], "us_per_layer_p50": ze["us_per_layer_p50"],
                    "dispatch_us": ze["dispatch_us"], "combine_us": ze["combine_us"],
-                   "rows_received_rank0": rows, "payload": "bf16",
+                   "rows_received_rank0": rows, "payload": "bf16", "kernel_us": ekt,
                    "how": "ElasticBuffer.dispatch(do_cpu_sync=False) + ElasticBuffer.combine on the "
                           "headline's inputs, identity expert, timed like the headline"}
         if R > 1 and rank == 0:

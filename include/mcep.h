@@ -363,6 +363,8 @@ typedef struct mcep_elastic_dispatch_args {
     int64_t* recv_topk_idx;
     float* recv_topk_weights;    /* or NULL */
     int32_t* recv_src_metadata;
+    int64_t* copied_topk_idx;    /* [num_tokens][num_topk] or NULL: receives a copy of topk_idx for the handle
+                                  * (the reference's kernel has the same output, dispatch_official.cuh:397-399) */
 } mcep_elastic_dispatch_args;
 int mcep_elastic_dispatch(mcep_buffer* buf, const mcep_elastic_dispatch_args* args,
                           mcep_event** out_event);

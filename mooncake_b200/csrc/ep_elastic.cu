@@ -7,8 +7,9 @@
 // reach); the kernels of ep_elastic_kernels.cu prepare that routing and turn the
 // exchange's outputs into the tensors of the elastic interface. What the
 // receiver needs to know about a row beyond its payload (the token's expert
-// choices and weights) is not sent with it: the source leaves a record per token
-// in its symmetric memory and the receiver reads the records of the rows it got.
+// choices, weights and index) travels ahead of it: before the exchange starts,
+// the source stores a record per row in the receiver's symmetric memory, at the
+// position the row will take inside the source's segment.
 #include "ep_elastic.cuh"
 
 #include <cstdio>
@@ -46,8 +47,8 @@ using mcep::report_failure;
 
 size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-int record_stride(int K, int P) { return (int)up(8 * (size_t)K + 4 * (size_t)P, 16); }
-size_t record_bytes(int M, int K, int P) { return up((size_t)M * record_stride(K, P), 256); }
+int record_stride(int K, int P) { return (int)up(8 * (size_t)K + 4 + 4 * (size_t)P, 16); }
+size_t record_bytes(int R, int M, int K, int P) { return up((size_t)R * M * record_stride(K, P), 256); }
 
 // What the entry points keep per buffer between calls.
 struct ElasticState {
@@ -113,7 +114,7 @@ int ensure(ElasticState* s, const mcep::BufferView& v, int M, int K, int L, int 
     for (int p = 0; p < 2; ++p) {
         o_src[p] = take(RM * 4), o_lr[p] = take((size_t)R * 8), o_cnt[p] = take(64);
         o_topk[p] = take((size_t)M * K * 8);
-        o_rec[p] = v.group ? 0 : take(record_bytes(M, K, 0));
+        o_rec[p] = v.group ? 0 : take(record_bytes(R, M, K, 0));
     }
     const size_t o_ones = take((size_t)M * K * 4), o_fw = take(RM * K * 4);
     const size_t o_ps = take((size_t)(L + 1) * 4), o_hist = take((size_t)L * 4 + 4), o_tick = take(64);
@@ -201,7 +202,7 @@ extern "C" {
 
 uint64_t mcep_elastic_buffer_size_hint(int M, int hidden, int num_ranks, int num_topk) {
     if (M <= 0 || hidden <= 0 || num_ranks <= 0 || num_topk <= 0) return 0;
-    return mcep::exchange_bytes(num_ranks, num_ranks, M, hidden) + 2 * record_bytes(M, num_topk, 0);
+    return mcep::exchange_bytes(num_ranks, num_ranks, M, hidden) + 2 * record_bytes(num_ranks, M, num_topk, 0);
 }
 
 int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, mcep_event** out_event) {
@@ -221,7 +222,7 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
     EL_REQUIRE(a->psum_num_recv_tokens_per_expert != nullptr && (T == 0 || a->dst_buffer_slot_idx != nullptr));
     EL_REQUIRE(a->recv_x != nullptr && a->recv_topk_idx != nullptr && a->recv_src_metadata != nullptr);
     const int L = E / R;
-    const size_t rec_bytes = record_bytes(M, K, 0);
+    const size_t rec_bytes = record_bytes(R, M, K, 0);
     if (v.group && mcep::exchange_bytes(R, R, M, H) + 2 * rec_bytes > (size_t)v.num_bytes) {
         char m[256];
         snprintf(m, sizeof(m),
@@ -242,7 +243,8 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
     rp.topk_idx = a->topk_idx, rp.topk_weights = a->topk_weights;
     rp.T = T, rp.K = K, rp.E = E, rp.R = R, rp.M = M, rp.P = 0, rp.rank = v.rank;
     rp.rank_topk = s->rank_topk[par], rp.dst_slot = a->dst_buffer_slot_idx;
-    rp.records = static_cast<char*>(s->table_host[(size_t)par * R + v.rank]);
+    rp.copied_topk_idx = a->copied_topk_idx;
+    rp.record_base = s->record_table + (size_t)par * R;
     rp.record_stride = record_stride(K, 0);
     EL_CUDA(mcep::launch_elastic_route(rp, stream));
 
@@ -267,6 +269,8 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
     da.compute_stream = reinterpret_cast<uint64_t>(stream);
     mcep_event* ev = nullptr;
     mcep_hook* hook = nullptr;
+    // the route kernel lets its dependents start early; the exchange's first kernel waits for it
+    mcep::allow_chained_first_launch(b);
     if (int rc = mcep_dispatch(b, &da, &ev, &hook)) return rc;
 
     auto& rec = s->rec[par];
@@ -274,8 +278,9 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
     rec.expand = a->do_expand != 0, rec.stamp = ++s->clock;
 
     mcep::ElasticEpilogueParams ep = {};
-    ep.layout_range = s->layout_range[par], ep.src_info = s->src_info[par];
-    ep.record_base = s->record_table + (size_t)par * R, ep.record_stride = rp.record_stride;
+    ep.layout_range = s->layout_range[par];
+    ep.records = static_cast<const char*>(s->table_host[(size_t)par * R + v.rank]);
+    ep.record_stride = rp.record_stride;
     ep.R = R, ep.M = M, ep.K = K, ep.L = L, ep.P = 0, ep.rank = v.rank;
     ep.alignment = a->expert_alignment, ep.expand = a->do_expand != 0;
     ep.recv_topk_idx = a->recv_topk_idx;
@@ -298,8 +303,9 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
 
     const int num_sms = v.num_sms;
     const bool expand = a->do_expand != 0;
+    const bool pdl = !v.defer;
     auto after = [=]() -> int {
-        EL_CUDA(mcep::launch_elastic_epilogue(ep, num_sms, stream));
+        EL_CUDA(mcep::launch_elastic_epilogue(ep, num_sms, stream, pdl));
         if (expand) {
             EL_CUDA(mcep::launch_elastic_expand_scan(xp, stream));
             EL_CUDA(mcep::launch_elastic_expand_copy(xp, num_sms, stream));

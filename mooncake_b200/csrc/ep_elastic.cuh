@@ -17,9 +17,10 @@
 
 namespace mcep {
 
-// Per source token, readable by every peer until the second dispatch after the
-// one that wrote it: [K] int32 expert choices, [K] fp32 weights, [P] 4-byte
-// scale packs. `record_stride` bytes apart.
+// A record per row a rank is about to receive, stored by the source in the
+// receiver's memory at [source rank][position among the source's rows]:
+// [K] int32 expert choices, [K] fp32 weights, int32 token index at the source,
+// [P] 4-byte scale packs. `record_stride` bytes apart; one set per parity.
 struct ElasticRouteParams {
     const int64_t* topk_idx;     // [T][K]
     const float* topk_weights;   // [T][K] or null
@@ -28,15 +29,15 @@ struct ElasticRouteParams {
     int T, K, E, R, M, P, rank;
     int64_t* rank_topk;          // [T][K] destination rank at its last listing inside the token, else -1
     int32_t* dst_slot;           // [T][K] rank * M + position among this rank's tokens for that destination, else -1
-    char* records;               // this rank's records (symmetric memory in a group)
+    int64_t* copied_topk_idx;    // [T][K] copy of topk_idx kept with the handle, or null
+    void* const* record_base;    // [R] every rank's record area of this call's parity (null: not mapped)
     int record_stride;
 };
 cudaError_t launch_elastic_route(const ElasticRouteParams& p, cudaStream_t stream);
 
 struct ElasticEpilogueParams {
     const int64_t* layout_range;  // [R] (begin << 32) | count, as the exchange left it
-    const int32_t* src_info;      // [R*M] token index at the source
-    void* const* record_base;     // [R] every rank's records
+    const char* records;          // this rank's record area of this call's parity
     int record_stride;
     int R, M, K, L, P, rank;
     int alignment;                // expert_alignment
@@ -52,7 +53,8 @@ struct ElasticEpilogueParams {
     unsigned* ticket;             // scratch word, zero between calls
     int32_t* status;
 };
-cudaError_t launch_elastic_epilogue(const ElasticEpilogueParams& p, int num_sms, cudaStream_t stream);
+cudaError_t launch_elastic_epilogue(const ElasticEpilogueParams& p, int num_sms, cudaStream_t stream,
+                                    bool pdl);
 
 // Expanded layout: one row per (received token, local expert it chose), experts'
 // segments starting at psum_start[e], rows of one expert in receive order.

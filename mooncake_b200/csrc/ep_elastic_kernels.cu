@@ -22,14 +22,14 @@ __device__ __forceinline__ int rows_received(const int64_t* layout_range, int R,
         if (s_begin) s_begin[r] = begin;
         if (s_end) s_end[r] = begin + cnt;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32) {
         int n = 0;
-        for (int r = 0; r < R; ++r) {
+        for (int r = threadIdx.x; r < R; r += 32) {
             const int64_t v = layout_range[r];
             n = max(n, (int)(v >> 32) + (int)(v & 0xffffffffll));
         }
-        s_n = n;
+        for (int d = 16; d > 0; d >>= 1) n = max(n, __shfl_xor_sync(kAll, n, d));
+        if (threadIdx.x == 0) s_n = n;
     }
     __syncthreads();
     return s_n;
@@ -59,55 +59,70 @@ __device__ __forceinline__ int block_position(bool flag, int* s_warp, int* s_bas
 // top-k list (the last one that names an expert of r, as `deduplicate` of
 // mooncake_ep_elastic_ptx.cuh:690-693 elects), and in which position (token
 // order, as the deterministic prologue of the reference assigns them:
-// mooncake_ep_elastic_dispatch_deterministic_prologue.cuh:134-166). Block 0 also
-// writes the per-token records the receivers read.
+// mooncake_ep_elastic_dispatch_deterministic_prologue.cuh:134-166). The block
+// also stores, in rank r's memory, the record of every row r is about to get.
 __global__ void __launch_bounds__(kThreads) ep_elastic_route_kernel(ElasticRouteParams p) {
     const int r = blockIdx.x;
     const int L = p.E / p.R;
+    pdl_launch_dependents();  // the exchange's first kernel may take its place; it waits for this one at its top
     __shared__ int s_warp[kWarps];
     __shared__ int s_base;
     if (threadIdx.x == 0) s_base = 0;
     __syncthreads();
     for (int t0 = 0; t0 < p.T; t0 += kThreads) {
         const int t = t0 + threadIdx.x;
+        // the token's choices, all loaded before anything is stored
+        int64_t raw[kMaxTopk];
+        int rk[kMaxTopk];
         int master = -1;
         if (t < p.T) {
-            char* rec = p.records + (size_t)t * p.record_stride;
-            for (int k = 0; k < p.K; ++k) {
-                const int64_t e = p.topk_idx[(size_t)t * p.K + k];
-                const bool valid = e >= 0 && e < p.E;
-                const int rk = valid ? (int)(e / L) : -1;
-                if (rk == r) master = k;
-                if (r == 0) {
-                    if (!valid) {
-                        p.rank_topk[(size_t)t * p.K + k] = -1;
-                        p.dst_slot[(size_t)t * p.K + k] = -1;
-                    }
-                    reinterpret_cast<int32_t*>(rec)[k] = valid ? (int32_t)e : -1;
-                    reinterpret_cast<float*>(rec)[p.K + k] =
-                        p.topk_weights ? p.topk_weights[(size_t)t * p.K + k] : 0.f;
-                }
-            }
-            if (r == 0 && p.P > 0) {
-                const uint32_t* sf = reinterpret_cast<const uint32_t*>(p.sf) + (size_t)t * p.sf_token_stride;
-                uint32_t* out = reinterpret_cast<uint32_t*>(rec) + 2 * p.K;
-                for (int j = 0; j < p.P; ++j) out[j] = sf[(size_t)j * p.sf_hidden_stride];
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k) raw[k] = k < p.K ? __ldg(p.topk_idx + (size_t)t * p.K + k) : -1;
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k) {
+                rk[k] = (raw[k] >= 0 && raw[k] < p.E) ? (int)raw[k] / L : -1;
+                if (rk[k] == r) master = k;
             }
         }
         const int slot = block_position(master >= 0, s_warp, &s_base);
-        if (t < p.T && master >= 0) {
-            for (int k = 0; k < p.K; ++k) {
-                const int64_t e = p.topk_idx[(size_t)t * p.K + k];
-                if (e < 0 || e >= p.E || (int)(e / L) != r) continue;
-                p.rank_topk[(size_t)t * p.K + k] = (k == master) ? r : -1;
-                p.dst_slot[(size_t)t * p.K + k] = (k == master) ? p.rank * p.M + slot : -1;
+        if (t >= p.T) continue;
+#pragma unroll
+        for (int k = 0; k < kMaxTopk; ++k) {
+            if (k >= p.K) break;
+            const size_t at = (size_t)t * p.K + k;
+            if (rk[k] == r) {
+                p.rank_topk[at] = (k == master) ? r : -1;
+                p.dst_slot[at] = (k == master) ? p.rank * p.M + slot : -1;
+            } else if (rk[k] < 0 && r == 0) {
+                p.rank_topk[at] = -1;
+                p.dst_slot[at] = -1;
             }
+        }
+        // what the receiver needs to know about the row, stored where it will look for it:
+        // in rank r's memory, at this rank's region, at the row's position
+        char* base = static_cast<char*>(p.record_base[r]);
+        if (master >= 0 && base != nullptr) {
+            char* rec = base + ((size_t)p.rank * p.M + slot) * p.record_stride;
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k) {
+                if (k >= p.K) break;
+                reinterpret_cast<int32_t*>(rec)[k] = rk[k] >= 0 ? (int32_t)raw[k] : -1;
+                reinterpret_cast<float*>(rec)[p.K + k] =
+                    p.topk_weights ? __ldg(p.topk_weights + (size_t)t * p.K + k) : 0.f;
+            }
+            reinterpret_cast<int32_t*>(rec)[2 * p.K] = t;
+        }
+        if (r != 0 || p.copied_topk_idx == nullptr) continue;
+#pragma unroll
+        for (int k = 0; k < kMaxTopk; ++k) {
+            if (k >= p.K) break;
+            p.copied_topk_idx[(size_t)t * p.K + k] = raw[k];
         }
     }
 }
 
-// Receiver side, after the exchange: per received row the source's record is
-// read from the source's memory and turned into the row's local expert choices,
+// Receiver side, after the exchange: per received row the record its source
+// stored here is turned into the row's local expert choices,
 // weights and source metadata (mooncake_ep_elastic_dispatch_copy_epilogue.cuh:
 // 114-132, 212-248); the last block to finish turns the per-expert hit counts
 // into the aligned exclusive prefix sum of
@@ -116,6 +131,7 @@ __global__ void __launch_bounds__(kThreads) ep_elastic_epilogue_kernel(ElasticEp
     __shared__ int s_begin[kMaxRanks], s_end[kMaxRanks];
     __shared__ bool s_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_wait();  // the exchange's kernels wrote the layout
     const int n = rows_received(p.layout_range, p.R, s_begin, s_end);
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         int run = 0;
@@ -134,17 +150,18 @@ __global__ void __launch_bounds__(kThreads) ep_elastic_epilogue_kernel(ElasticEp
             if (b) src = r0 + __ffs(b) - 1;
         }
         if (src < 0) continue;
-        const int tok = p.src_info[i];
-        if (tok < 0 || tok >= p.M) {
-            if (lane == 0) atomicOr(p.status, kStatusBadSource);
-            continue;
-        }
-        const char* rec = static_cast<const char*>(p.record_base[src]) + (size_t)tok * p.record_stride;
+        // the record the source stored for its (i - begin)-th row, in this rank's memory
+        const char* rec = p.records + ((size_t)src * p.M + (i - s_begin[src])) * p.record_stride;
         int e = -1;
         float w = 0.f;
         if (lane < p.K) {
             e = ld_s32_coherent(rec + 4 * lane);
             w = ld_f32_coherent(rec + 4 * (p.K + lane));
+        }
+        const int tok = ld_s32_coherent(rec + 8 * p.K);
+        if (tok < 0 || tok >= p.M) {
+            if (lane == 0) atomicOr(p.status, kStatusBadSource);
+            continue;
         }
         const int local = (e >= lo && e < lo + p.L) ? e - lo : -1;
         const unsigned hit = __ballot_sync(kAll, local >= 0);
@@ -162,7 +179,7 @@ __global__ void __launch_bounds__(kThreads) ep_elastic_epilogue_kernel(ElasticEp
         if (p.recv_sf)
             for (int j = lane; j < p.P; j += 32)
                 reinterpret_cast<int32_t*>(p.recv_sf)[(size_t)i * p.P + j] =
-                    ld_s32_coherent(rec + 8 * p.K + 4 * j);
+                    ld_s32_coherent(rec + 8 * p.K + 4 + 4 * j);
     }
     __threadfence();
     __syncthreads();
@@ -316,12 +333,22 @@ cudaError_t launch_elastic_route(const ElasticRouteParams& p, cudaStream_t strea
     return scope.done(cudaGetLastError());
 }
 
-cudaError_t launch_elastic_epilogue(const ElasticEpilogueParams& p, int num_sms, cudaStream_t stream) {
+cudaError_t launch_elastic_epilogue(const ElasticEpilogueParams& p, int num_sms, cudaStream_t stream,
+                                    bool pdl) {
     const int cap_blocks = (p.R * p.M + kWarps - 1) / kWarps;
     const int grid = max(1, min(2 * num_sms, cap_blocks));
     LaunchScope scope("ep_elastic_epilogue", stream);
-    ep_elastic_epilogue_kernel<<<grid, kThreads, 0, stream>>>(p);
-    return scope.done(cudaGetLastError());
+    // with `pdl` the blocks may become resident while the exchange's last kernel drains;
+    // they wait for its completion before they read anything
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid), cfg.blockDim = dim3(kThreads), cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr, cfg.numAttrs = 1;
+    }
+    return scope.done(cudaLaunchKernelEx(&cfg, ep_elastic_epilogue_kernel, p));
 }
 
 cudaError_t launch_elastic_expand_scan(const ElasticExpandParams& p, cudaStream_t stream) {

@@ -249,6 +249,7 @@ struct mcep_buffer {
         mcep::GroupCombineParams c;
     } pending;
     std::function<int()> after_deferred;  // run once the prepared dispatch has been launched
+    bool chain_first_once = false;        // see allow_chained_first_launch
 
     // what combine needs to know about the dispatch call a handle came from
     struct DispatchRecord {
@@ -344,6 +345,8 @@ size_t exchange_bytes(int num_ranks, int num_experts, int M, int hidden) {
 }
 
 void set_after_deferred(mcep_buffer* b, std::function<int()> fn) { b->after_deferred = std::move(fn); }
+
+void allow_chained_first_launch(mcep_buffer* b) { b->chain_first_once = true; }
 
 int report_failure(int code, const char* message) { return fail(code, "%s", message); }
 
@@ -867,8 +870,10 @@ int mcep_dispatch(mcep_buffer* b, const mcep_dispatch_args* a, mcep_event** out_
     if (a->async_finish)
         if (int rc = order_after(stream, compute, b->ev_a)) return rc;
 
-    mcep::LaunchCtx first{stream, b->num_sms, false};
     const bool pdl = chain_with_pdl(b, stream) && chain_with_pdl(b, compute);
+    const bool chain_first = b->chain_first_once && pdl && !b->defer;
+    b->chain_first_once = false;
+    mcep::LaunchCtx first{stream, b->num_sms, chain_first};
     mcep::LaunchCtx next{stream, b->num_sms, pdl};
 
     const bool fused = mcep::can_fuse_layout(T, K, E, b->num_sms) && b->fuse_layout;

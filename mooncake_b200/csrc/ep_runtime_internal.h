@@ -32,6 +32,12 @@ size_t exchange_bytes(int num_ranks, int num_experts, int M, int hidden);
 // has been launched (run once, then forgotten).
 void set_after_deferred(mcep_buffer* b, std::function<int()> fn);
 
+// The first kernel of the buffer's NEXT dispatch call may be launched with
+// programmatic stream serialisation: the caller has just queued, on the same
+// stream, a kernel that lets its dependents start early and whose outputs that
+// first kernel reads only after waiting for it (all first kernels wait at their top).
+void allow_chained_first_launch(mcep_buffer* b);
+
 // Records the message mcep_last_error() returns and hands `code` back.
 int report_failure(int code, const char* message);
 

@@ -62,6 +62,7 @@ class _ElasticDispatchArgs(_c.Structure):
         ("psum_num_recv_tokens_per_expert", _c.c_void_p), ("dst_buffer_slot_idx", _c.c_void_p),
         ("recv_x", _c.c_void_p), ("recv_x_scales", _c.c_void_p), ("recv_topk_idx", _c.c_void_p),
         ("recv_topk_weights", _c.c_void_p), ("recv_src_metadata", _c.c_void_p),
+        ("copied_topk_idx", _c.c_void_p),
     ]
 
 
@@ -390,8 +391,8 @@ class Buffer:
                          cached_mode: bool, psum_rank_ptr: int, psum_expert_ptr: int,
                          dst_buffer_slot_idx_ptr: int, recv_x_ptr: int, recv_x_scales_ptr: int,
                          recv_topk_idx_ptr: int, recv_topk_weights_ptr: int,
-                         recv_src_metadata_ptr: int, timeout_us: int = -1
-                         ) -> Optional[EventHandle]:
+                         recv_src_metadata_ptr: int, timeout_us: int = -1,
+                         copied_topk_idx_ptr: int = 0) -> Optional[EventHandle]:
         a = _ElasticDispatchArgs()
         a.x, a.x_element_size, a.sf = x_ptr, x_element_size, sf_ptr or None
         a.num_tokens, a.hidden, a.num_sf_packs = num_tokens, hidden, num_sf_packs
@@ -408,6 +409,7 @@ class Buffer:
         a.recv_x, a.recv_x_scales = recv_x_ptr, recv_x_scales_ptr or None
         a.recv_topk_idx, a.recv_topk_weights = recv_topk_idx_ptr, recv_topk_weights_ptr or None
         a.recv_src_metadata = recv_src_metadata_ptr
+        a.copied_topk_idx = copied_topk_idx_ptr or None
         ev = _c.c_void_p()
         _check(_lib.mcep_elastic_dispatch(self._h, _c.byref(a), _c.byref(ev)))
         return EventHandle(_adopt=ev.value) if ev.value else None

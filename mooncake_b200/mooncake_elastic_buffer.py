@@ -14,19 +14,23 @@ a caller can see:
 * one NVLink domain only: `num_scaleout_ranks` is always 1 (no hybrid mode);
 * bf16 payloads only; an `(x_fp8, scale_packs)` tuple raises NotImplementedError;
 * a cached handle recomputes the same layout from the handle's `topk_idx`
-  instead of reusing slot indices, so it carries no restriction on `do_expand`.
+  instead of reusing slot indices, so it carries no restriction on `do_expand`;
+* in a group, without `do_expand`, `recv_x` is by default a view of the buffer's
+  symmetric memory (peers store the rows there; nothing is copied on the
+  receiving side) and stays valid until the dispatch call after the next one on
+  the same buffer; `ElasticBuffer(..., recv_in_place=False)` returns a tensor of
+  its own instead (one more pass over the rows).
 """
 from __future__ import annotations
 
 import os
-import warnings
 from typing import Any, List, Optional, Tuple, Union
 
 import torch
 import torch.distributed as dist
 
 from . import ep
-from .mooncake_ep_buffer import EventOverlap, _stream_ptr
+from .mooncake_ep_buffer import EventOverlap, _DeviceBytes, _stream_ptr
 
 
 def _ceil_div(x: int, y: int) -> int:
@@ -72,12 +76,15 @@ class ElasticBuffer:
                  allow_hybrid_mode: bool = True, allow_multiple_reduction: bool = True,
                  prefer_overlap_with_compute: bool = True, sl_idx: int = 3,
                  num_allocated_qps: int = 0, num_cpu_timeout_secs: int = 300,
-                 num_gpu_timeout_secs: int = 100, explicitly_destroy: bool = False) -> None:
+                 num_gpu_timeout_secs: int = 100, explicitly_destroy: bool = False,
+                 recv_in_place: bool = True) -> None:
         if not allow_multiple_reduction:
             raise NotImplementedError("ElasticBuffer supports only allow_multiple_reduction=True")
         if use_fp8_dispatch:
             raise NotImplementedError("ElasticBuffer (B200): pre-quantised dispatch is not built; "
                                       "dispatch bf16")
+        self.recv_in_place = recv_in_place
+        self._views: dict = {}
         self.group = group
         self.backend = group
         self.rank_idx = group.rank()
@@ -162,6 +169,15 @@ class ElasticBuffer:
         if with_cpu_sync:
             torch.cuda.synchronize()
 
+    def _symmetric_tensor(self, ptr: int, nbytes: int, shape: tuple, device: torch.device) -> torch.Tensor:
+        """A bf16 tensor over `nbytes` of symmetric memory at `ptr` (made once per span)."""
+        key = (ptr, nbytes, shape)
+        t = self._views.get(key)
+        if t is None:
+            raw = torch.as_tensor(_DeviceBytes(self.runtime, ptr, nbytes), device=device)
+            t = self._views[key] = raw.view(torch.bfloat16).view(shape)
+        return t
+
     def _timeout_us(self) -> int:
         return -1 if self.num_gpu_timeout_secs < 0 else int(self.num_gpu_timeout_secs) * 1_000_000
 
@@ -215,23 +231,32 @@ class ElasticBuffer:
         psum_expert = torch.empty(L + 1, dtype=torch.int32, device=dev)
         psum_rank = torch.empty(self.num_scaleup_ranks, dtype=torch.int32, device=dev)
         dst_buffer_slot_idx = torch.empty((T, K), dtype=torch.int32, device=dev)
-        recv_x = torch.empty((out_cap, H), dtype=x.dtype, device=dev)
+        recv_x = None
+        if self.recv_in_place and not do_expand:
+            # where the exchange lands the rows: the flat tensor itself
+            ptr, nbytes = self.runtime.next_recv_x(num_max_tokens_per_rank, H, self.num_ranks, False)
+            if ptr:
+                recv_x = self._symmetric_tensor(ptr, nbytes, (n_cap, H), dev)
+        if recv_x is None:
+            recv_x = torch.empty((out_cap, H), dtype=x.dtype, device=dev)
         recv_topk_idx = torch.empty((n_cap, K), dtype=topk_idx.dtype, device=dev)
         recv_topk_weights = (torch.empty((out_cap,) if do_expand else (n_cap, K), dtype=torch.float32,
                                          device=dev) if topk_weights is not None else None)
         recv_src_metadata = torch.empty((n_cap, K + 2), dtype=torch.int32, device=dev)
         if topk_weights is not None:
             assert topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()
-        # the handle keeps its own copy of the routing, as the reference's does (:679)
-        kept_idx = handle.topk_idx if handle is not None else topk_idx.clone()
+        # the handle keeps its own copy of the routing, as the reference's does (:679); the
+        # copy is written by the call's first kernel
+        kept_idx = handle.topk_idx if handle is not None else torch.empty_like(topk_idx)
         event = self.runtime.elastic_dispatch(
-            x.data_ptr(), x.element_size(), 0, T, H, 0, 0, 0, kept_idx.data_ptr(), K,
+            x.data_ptr(), x.element_size(), 0, T, H, 0, 0, 0, topk_idx.data_ptr(), K,
             0 if topk_weights is None else topk_weights.data_ptr(), active_ranks.data_ptr(),
             num_experts, num_max_tokens_per_rank, expert_alignment, do_expand,
             async_with_compute_stream, _stream_ptr(), handle is not None, psum_rank.data_ptr(),
             psum_expert.data_ptr(), dst_buffer_slot_idx.data_ptr(), recv_x.data_ptr(), 0,
             recv_topk_idx.data_ptr(), 0 if recv_topk_weights is None else recv_topk_weights.data_ptr(),
-            recv_src_metadata.data_ptr(), self._timeout_us())
+            recv_src_metadata.data_ptr(), self._timeout_us(),
+            0 if handle is not None else kept_idx.data_ptr())
         handle_psum_expert = psum_expert if do_expand else psum_expert[1:]
 
         counts: List[int] = []
@@ -259,7 +284,7 @@ class ElasticBuffer:
         out_handle = EPHandle(do_expand, num_experts, expert_alignment, num_max_tokens_per_rank,
                               num_sms, kept_idx, counts, psum_rank, handle_psum_expert,
                               recv_src_metadata, dst_buffer_slot_idx, None, None, native_handle=True)
-        keep = (x, kept_idx, active_ranks, recv_x, recv_topk_idx, psum_rank, psum_expert,
+        keep = (x, topk_idx, kept_idx, active_ranks, recv_x, recv_topk_idx, psum_rank, psum_expert,
                 recv_src_metadata, dst_buffer_slot_idx) + \
             (() if topk_weights is None else (topk_weights, recv_topk_weights))
         return (recv_x, recv_topk_idx, recv_topk_weights, out_handle,

@@ -238,8 +238,8 @@ def test_elastic_wrapper_surface_and_loud_failure_without_a_gpu():
         ElasticBuffer(Solo(), allow_multiple_reduction=False)
     assert ElasticBuffer.get_buffer_size_hint(Solo(), 128, 4096, 8) == 0
     from mooncake_b200 import ep
-    # 2 parities x R*M rows x (32 + 4H) bytes, plus the per-token records
-    assert ep.elastic_buffer_size_hint(128, 4096, 8, 8) == 2 * 8 * 128 * (32 + 4 * 4096) + 2 * 128 * 64
+    # 2 parities x R*M rows x (32 + 4H) bytes, plus an 80-byte record per row (8K + 4, 16-byte aligned)
+    assert ep.elastic_buffer_size_hint(128, 4096, 8, 8) == 2 * 8 * 128 * (32 + 4 * 4096) + 2 * 8 * 128 * 80
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError, match="Failed: CUDA error"):
             ElasticBuffer(Solo(), num_max_tokens_per_rank=16, hidden=256, num_topk=2)

@@ -38,14 +38,15 @@ def _dispatch(bufs, xs, idxs, ws, E, M, alignment, expand, keep):
             recv_idx=torch.full((n_cap, K), -7, dtype=torch.int64, device="cuda"),
             recv_w=None if ws is None else torch.full((out_cap,) if expand else (n_cap, K), -7.0,
                                                       device="cuda"),
-            md=torch.full((n_cap, K + 2), -7, dtype=torch.int32, device="cuda"))
+            md=torch.full((n_cap, K + 2), -7, dtype=torch.int32, device="cuda"),
+            copied=torch.full((T, K), -7, dtype=torch.int64, device="cuda"))
         ev = bufs[r].runtime.elastic_dispatch(
             d["x"].data_ptr(), 2, 0, T, H, 0, 0, 0, d["idx"].data_ptr(), K,
             0 if ws is None else d["w"].data_ptr(), d["active"].data_ptr(), E, M, alignment, expand,
             False, torch.cuda.current_stream().cuda_stream, False, d["psum_rank"].data_ptr(),
             d["psum_expert"].data_ptr(), d["slot"].data_ptr(), d["recv_x"].data_ptr(), 0,
             d["recv_idx"].data_ptr(), 0 if ws is None else d["recv_w"].data_ptr(), d["md"].data_ptr(),
-            200_000)
+            200_000, d["copied"].data_ptr())
         assert ev is None
         outs.append(d)
     ep.launch_deferred([b.runtime for b in bufs])
@@ -78,6 +79,7 @@ def _check_dispatch(outs, want, expand, with_w, K):
         assert d["psum_rank"].cpu().tolist() == o["psum_rank"].tolist(), r
         assert d["psum_expert"].cpu().tolist() == o["psum_expert"].tolist(), r
         assert torch.equal(d["slot"].cpu(), o["dst_buffer_slot_idx"]), r
+        assert torch.equal(d["copied"], d["idx"]), r
         assert torch.equal(d["recv_idx"][:n].cpu(), o["recv_topk_idx"]), r
         assert torch.equal(d["md"][:n, :2].cpu(), o["recv_src_metadata"][:, :2]), r
         # rows beyond the received ones are left alone

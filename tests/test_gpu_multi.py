@@ -77,7 +77,11 @@ def test_fabric_handle_mode_two_gpus():
 def test_multi_gpu_parity(R):
     if torch.cuda.device_count() < R:
         pytest.skip(f"needs {R} GPUs")
-    _run_workers(R, _cases(R), {}, f"multi_gpu_parity_r{R}.log", port=29620 + R)
+    cases = _cases(R)
+    only = os.environ.get("MCEP_TEST_ONLY", "")  # e.g. "elastic": the cases whose name contains it
+    if only:
+        cases = {k: v for k, v in cases.items() if only in k}
+    _run_workers(R, cases, {}, f"multi_gpu_parity_r{R}.log", port=29620 + R)
 
 
 def _run_workers(R, cases, extra_env, log_name, port):
