@@ -173,7 +173,7 @@ def test_every_entry_point_cites_what_it_replaces():
 
 
 def test_library_is_rebuilt_when_its_sources_change(tmp_path, monkeypatch):
-    """The library is judged stale by the CONTENT of its sources (a digest kept
+    """The library counts as stale by the CONTENT of its sources (a digest kept
     beside it), not by file times: a copy of the tree keeps no times, and a
     library older than its sources must not be loaded in silence."""
     from mooncake_b200 import build
