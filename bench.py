@@ -787,19 +787,24 @@ def run_ours(args):
     # ---- the elastic-style interface on the same inputs ------------------------------------
     elastic = None
     if not args.no_extras and inactive < 0 and not args.force_staged and w["T"] <= 1024:
-        elayer = Layer(args, w, group, rank, R, dev, zero_copy=False) if prefill is not None else layer
-        tde, tce, rows, ekt = elastic_block(w, elayer, group, rank, R, dev, flush, sync_word,
-                                            max(10, K_steps // 2))
-        ze = summarise(tde, tce, dev, R)
-        elastic = {"us_per_layer": ze["us_per_layer"], "us_per_layer_p50": ze["us_per_layer_p50"],
-                   "dispatch_us": ze["dispatch_us"], "combine_us": ze["combine_us"],
-                   "rows_received_rank0": rows, "payload": "bf16", "kernel_us": ekt,
-                   "how": "ElasticBuffer.dispatch(do_cpu_sync=False) + ElasticBuffer.combine on the "
-                          "headline's inputs, identity expert, timed like the headline"}
-        if R > 1 and rank == 0:
-            us, nrows = elastic_nvlink_us(w, R, idx_all)
-            elastic.update({"nvlink_roofline_us": us, "rows_busiest_gpu": nrows,
-                            "nvlink_frac_of_peak": us / ze["us_per_layer"]})
+        # an extra beside the headline: an argument or state error here (raised alike on every
+        # rank, before anything is launched) must not cost the line its headline
+        try:
+            elayer = Layer(args, w, group, rank, R, dev, zero_copy=False) if prefill is not None else layer
+            tde, tce, rows, ekt = elastic_block(w, elayer, group, rank, R, dev, flush, sync_word,
+                                                max(10, K_steps // 2))
+            ze = summarise(tde, tce, dev, R)
+            elastic = {"us_per_layer": ze["us_per_layer"], "us_per_layer_p50": ze["us_per_layer_p50"],
+                       "dispatch_us": ze["dispatch_us"], "combine_us": ze["combine_us"],
+                       "rows_received_rank0": rows, "payload": "bf16", "kernel_us": ekt,
+                       "how": "ElasticBuffer.dispatch(do_cpu_sync=False) + ElasticBuffer.combine on the "
+                              "headline's inputs, identity expert, timed like the headline"}
+            if R > 1 and rank == 0:
+                us, nrows = elastic_nvlink_us(w, R, idx_all)
+                elastic.update({"nvlink_roofline_us": us, "rows_busiest_gpu": nrows,
+                                "nvlink_frac_of_peak": us / ze["us_per_layer"]})
+        except (RuntimeError, AssertionError) as exc:
+            elastic = {"error": str(exc)[:300]}
 
     if rank != 0:
         if R > 1:
