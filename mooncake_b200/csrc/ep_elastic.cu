@@ -76,6 +76,10 @@ struct ElasticState {
     } rec[2];
     uint64_t clock = 0;
     uint32_t calls = 0;
+    // The record areas sit at fixed places for the life of the buffer (fixed by its first
+    // elastic call): a peer may still be reading one call's records while the next call's are
+    // being stored, so the two areas must not move with the shapes of the calls.
+    size_t record_area_bytes = 0;
 };
 
 std::mutex g_mu;
@@ -222,7 +226,13 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
     EL_REQUIRE(a->psum_num_recv_tokens_per_expert != nullptr && (T == 0 || a->dst_buffer_slot_idx != nullptr));
     EL_REQUIRE(a->recv_x != nullptr && a->recv_topk_idx != nullptr && a->recv_src_metadata != nullptr);
     const int L = E / R;
-    const size_t rec_bytes = record_bytes(R, M, K, 0);
+    ElasticState* s = state_of(b);
+    const size_t rec_want = record_bytes(R, M, K, 0);
+    const size_t rec_bytes = (v.group && s->record_area_bytes != 0) ? s->record_area_bytes : rec_want;
+    if (rec_want > rec_bytes)
+        return report_failure(MCEP_ERR_INVALID,
+                              "Failed: Assertion error 'elastic calls of one buffer need no more record "
+                              "space (num_max_tokens_per_rank, num_topk) than its first elastic call'");
     if (v.group && mcep::exchange_bytes(R, R, M, H) + 2 * rec_bytes > (size_t)v.num_bytes) {
         char m[256];
         snprintf(m, sizeof(m),
@@ -231,11 +241,11 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
         return report_failure(MCEP_ERR_INVALID, m);
     }
 
-    ElasticState* s = state_of(b);
     cudaStream_t stream = nullptr;
     // the scratch is set up on the caller's stream, ahead of everything this call queues
     if (int rc = ensure(s, v, M, K, L, H, reinterpret_cast<cudaStream_t>(a->compute_stream))) return rc;
     if (int rc = pick_stream(s, v, a->async_with_compute_stream != 0, a->compute_stream, &stream)) return rc;
+    if (v.group) s->record_area_bytes = rec_bytes;
     const int par = (int)(++s->calls & 1u);
     if (int rc = refresh_record_table(s, v, par, rec_bytes)) return rc;
 

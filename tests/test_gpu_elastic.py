@@ -211,3 +211,9 @@ def test_elastic_argument_errors():
         bufs[0].runtime.elastic_combine(x.data_ptr(), 8, 256, idx.data_ptr(), 8, 4, 0,
                                         args["psum_rank"].data_ptr(), md.data_ptr(), act.data_ptr(), 8, 32,
                                         False, False, 0, out.data_ptr(), 1000)
+    # the first call that goes through fixes where the record areas sit; later calls may need less, not more
+    call()
+    call(M=16)
+    with pytest.raises(RuntimeError, match="no more record space"):
+        call(M=64)
+    torch.cuda.synchronize()
