@@ -47,8 +47,8 @@ using mcep::report_failure;
 
 size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-int record_stride(int K, int P) { return (int)up(8 * (size_t)K + 4 + 4 * (size_t)P, 16); }
-size_t record_bytes(int R, int M, int K, int P) { return up((size_t)R * M * record_stride(K, P), 256); }
+int record_stride(int K) { return (int)up(8 * (size_t)K + 4, 16); }
+size_t record_bytes(int R, int M, int K) { return up((size_t)R * M * record_stride(K), 256); }
 
 // What the entry points keep per buffer between calls.
 struct ElasticState {
@@ -118,7 +118,7 @@ int ensure(ElasticState* s, const mcep::BufferView& v, int M, int K, int L, int 
     for (int p = 0; p < 2; ++p) {
         o_src[p] = take(RM * 4), o_lr[p] = take((size_t)R * 8), o_cnt[p] = take(64);
         o_topk[p] = take((size_t)M * K * 8);
-        o_rec[p] = v.group ? 0 : take(record_bytes(R, M, K, 0));
+        o_rec[p] = v.group ? 0 : take(record_bytes(R, M, K));
     }
     const size_t o_ones = take((size_t)M * K * 4), o_fw = take(RM * K * 4);
     const size_t o_ps = take((size_t)(L + 1) * 4), o_hist = take((size_t)L * 4 + 4), o_tick = take(64);
@@ -206,7 +206,7 @@ extern "C" {
 
 uint64_t mcep_elastic_buffer_size_hint(int M, int hidden, int num_ranks, int num_topk) {
     if (M <= 0 || hidden <= 0 || num_ranks <= 0 || num_topk <= 0) return 0;
-    return mcep::exchange_bytes(num_ranks, num_ranks, M, hidden) + 2 * record_bytes(num_ranks, M, num_topk, 0);
+    return mcep::exchange_bytes(num_ranks, num_ranks, M, hidden) + 2 * record_bytes(num_ranks, M, num_topk);
 }
 
 int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, mcep_event** out_event) {
@@ -227,7 +227,7 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
     EL_REQUIRE(a->recv_x != nullptr && a->recv_topk_idx != nullptr && a->recv_src_metadata != nullptr);
     const int L = E / R;
     ElasticState* s = state_of(b);
-    const size_t rec_want = record_bytes(R, M, K, 0);
+    const size_t rec_want = record_bytes(R, M, K);
     const size_t rec_bytes = (v.group && s->record_area_bytes != 0) ? s->record_area_bytes : rec_want;
     if (rec_want > rec_bytes)
         return report_failure(MCEP_ERR_INVALID,
@@ -251,11 +251,11 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
 
     mcep::ElasticRouteParams rp = {};
     rp.topk_idx = a->topk_idx, rp.topk_weights = a->topk_weights;
-    rp.T = T, rp.K = K, rp.E = E, rp.R = R, rp.M = M, rp.P = 0, rp.rank = v.rank;
+    rp.T = T, rp.K = K, rp.E = E, rp.R = R, rp.M = M, rp.rank = v.rank;
     rp.rank_topk = s->rank_topk[par], rp.dst_slot = a->dst_buffer_slot_idx;
     rp.copied_topk_idx = a->copied_topk_idx;
     rp.record_base = s->record_table + (size_t)par * R;
-    rp.record_stride = record_stride(K, 0);
+    rp.record_stride = record_stride(K);
     EL_CUDA(mcep::launch_elastic_route(rp, stream));
 
     // the exchange: ranks as experts
@@ -291,11 +291,10 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
     ep.layout_range = s->layout_range[par];
     ep.records = static_cast<const char*>(s->table_host[(size_t)par * R + v.rank]);
     ep.record_stride = rp.record_stride;
-    ep.R = R, ep.M = M, ep.K = K, ep.L = L, ep.P = 0, ep.rank = v.rank;
+    ep.R = R, ep.M = M, ep.K = K, ep.L = L, ep.rank = v.rank;
     ep.alignment = a->expert_alignment, ep.expand = a->do_expand != 0;
     ep.recv_topk_idx = a->recv_topk_idx;
     ep.recv_topk_weights = a->do_expand ? s->flat_weights : a->recv_topk_weights;
-    ep.recv_sf = nullptr;
     ep.recv_src_metadata = a->recv_src_metadata;
     ep.psum_rank = a->psum_num_recv_tokens_per_scaleup_rank;
     ep.psum_expert = a->psum_num_recv_tokens_per_expert;
@@ -305,11 +304,11 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
     mcep::ElasticExpandParams xp = {};
     xp.layout_range = s->layout_range[par], xp.recv_topk_idx = a->recv_topk_idx;
     xp.flat_weights = a->recv_topk_weights ? s->flat_weights : nullptr;
-    xp.flat_sf = nullptr, xp.flat_x = flat;
-    xp.R = R, xp.K = K, xp.L = L, xp.P = 0, xp.row_bytes = 2 * H;
+    xp.flat_x = flat;
+    xp.R = R, xp.K = K, xp.L = L, xp.row_bytes = 2 * H;
     xp.psum_start = s->psum_start, xp.psum_expert = a->psum_num_recv_tokens_per_expert;
     xp.recv_src_metadata = a->recv_src_metadata, xp.recv_x = a->recv_x;
-    xp.recv_topk_weights = a->recv_topk_weights, xp.recv_sf = nullptr;
+    xp.recv_topk_weights = a->recv_topk_weights;
 
     const int num_sms = v.num_sms;
     const bool expand = a->do_expand != 0;

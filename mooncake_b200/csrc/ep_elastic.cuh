@@ -19,14 +19,12 @@ namespace mcep {
 
 // A record per row a rank is about to receive, stored by the source in the
 // receiver's memory at [source rank][position among the source's rows]:
-// [K] int32 expert choices, [K] fp32 weights, int32 token index at the source,
-// [P] 4-byte scale packs. `record_stride` bytes apart; one set per parity.
+// [K] int32 expert choices, [K] fp32 weights, int32 token index at the source.
+// `record_stride` bytes apart; one set per parity.
 struct ElasticRouteParams {
     const int64_t* topk_idx;     // [T][K]
     const float* topk_weights;   // [T][K] or null
-    const void* sf;              // [T][P] scale packs (4 bytes each) or null
-    int sf_token_stride, sf_hidden_stride;  // in packs
-    int T, K, E, R, M, P, rank;
+    int T, K, E, R, M, rank;
     int64_t* rank_topk;          // [T][K] destination rank at its last listing inside the token, else -1
     int32_t* dst_slot;           // [T][K] rank * M + position among this rank's tokens for that destination, else -1
     int64_t* copied_topk_idx;    // [T][K] copy of topk_idx kept with the handle, or null
@@ -39,12 +37,11 @@ struct ElasticEpilogueParams {
     const int64_t* layout_range;  // [R] (begin << 32) | count, as the exchange left it
     const char* records;          // this rank's record area of this call's parity
     int record_stride;
-    int R, M, K, L, P, rank;
+    int R, M, K, L, rank;
     int alignment;                // expert_alignment
     int expand;
     int64_t* recv_topk_idx;       // [n][K] local expert or -1
     float* recv_topk_weights;     // [n][K] or null (expand: scratch, scattered later)
-    void* recv_sf;                // [n][P] or null (expand: scratch)
     int32_t* recv_src_metadata;   // [n][K+2]
     int32_t* psum_rank;           // [R] inclusive
     int32_t* psum_expert;         // [L+1] exclusive, aligned counts
@@ -62,15 +59,13 @@ struct ElasticExpandParams {
     const int64_t* layout_range;  // [R]
     const int64_t* recv_topk_idx; // [n][K]
     const float* flat_weights;    // [n][K] or null
-    const void* flat_sf;          // [n][P] or null
     const void* flat_x;           // [n][row_bytes]
-    int R, K, L, P, row_bytes;
+    int R, K, L, row_bytes;
     const int32_t* psum_start;    // [L+1]
     int32_t* psum_expert;         // [L+1]: entries < L become the ends of the segments
     int32_t* recv_src_metadata;   // [n][K+2], columns 2.. written here
     void* recv_x;                 // [rows][row_bytes]
     float* recv_topk_weights;     // [rows] or null
-    void* recv_sf;                // [rows][P] or null
 };
 cudaError_t launch_elastic_expand_scan(const ElasticExpandParams& p, cudaStream_t stream);
 cudaError_t launch_elastic_expand_copy(const ElasticExpandParams& p, int num_sms, cudaStream_t stream);

@@ -176,10 +176,6 @@ __global__ void __launch_bounds__(kThreads) ep_elastic_epilogue_kernel(ElasticEp
             p.recv_src_metadata[(size_t)i * md_stride] = src * p.M + tok;
             p.recv_src_metadata[(size_t)i * md_stride + 1] = src * p.K + master;
         }
-        if (p.recv_sf)
-            for (int j = lane; j < p.P; j += 32)
-                reinterpret_cast<int32_t*>(p.recv_sf)[(size_t)i * p.P + j] =
-                    ld_s32_coherent(rec + 8 * p.K + 4 + 4 * j);
     }
     __threadfence();
     __syncthreads();
@@ -258,10 +254,6 @@ __global__ void __launch_bounds__(kThreads) ep_elastic_expand_copy_kernel(Elasti
             copy_row(static_cast<char*>(p.recv_x) + (size_t)dst * p.row_bytes, src, p.row_bytes, lane);
             if (p.recv_topk_weights && lane == 0)
                 p.recv_topk_weights[dst] = p.flat_weights[(size_t)i * p.K + k];
-            if (p.recv_sf)
-                for (int j = lane; j < p.P; j += 32)
-                    reinterpret_cast<int32_t*>(p.recv_sf)[(size_t)dst * p.P + j] =
-                        reinterpret_cast<const int32_t*>(p.flat_sf)[(size_t)i * p.P + j];
         }
     }
 }
