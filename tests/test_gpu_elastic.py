@@ -135,8 +135,7 @@ def test_elastic_calls_match_the_oracle(case):
     _check_dispatch(outs, want, expand, with_w, K)
 
     # combine: the mock expert scales every row by a factor of its rank
-    rows = [o["recv_x"] if not expand else o["recv_x"] for o in want]
-    ys_cpu = [_expert(rows[r], r) for r in range(R)]
+    ys_cpu = [_expert(want[r]["recv_x"], r) for r in range(R)]
     ys = [y.cuda() if y.shape[0] else torch.zeros((1, H), dtype=torch.bfloat16, device="cuda") for y in ys_cpu]
     got = _combine(bufs, ys, outs, E, M, expand)
     ref = eo.elastic_combine(ys_cpu, want, idxs, E, expand)
