@@ -1,7 +1,7 @@
 // A pybind11 binding of the C ABI (include/mcep.h) with the surface of the
-// reference's compiled module `mooncake._ep` for the legacy Buffer
-// (mooncake-ep/src/ep_py.cpp:14-46): `Buffer`, `EventHandle`,
-// `get_ep_buffer_size_hint`, `MAX_QP_COUNT`. It is what a maintainer who wants
+// reference's compiled module `mooncake._ep` (mooncake-ep/src/ep_py.cpp:14-87):
+// `Buffer`, `ElasticBuffer`, `EventHandle`, `get_ep_buffer_size_hint`,
+// `calculate_elastic_buffer_size`, `MAX_QP_COUNT`. It is what a maintainer who wants
 // to keep `_ep` a compiled module would put in place of ep_py.cpp; the package
 // itself uses the ctypes binding (mooncake_b200/ep.py) and does not need it.
 //
@@ -165,6 +165,95 @@ struct Buffer {  // mooncake-ep/include/mooncake_ep_buffer.h:65-195
     }
 };
 
+// mooncake-ep/include/elastic/mooncake_ep_elastic_buffer.h:38-110, for one NVLink domain
+struct ElasticBuffer : Buffer {
+    int rank;
+    int64_t gpu_timeout_secs;
+    ElasticBuffer(int rank_, int num_ranks_, int64_t num_buffer_bytes, int64_t /*num_max_tokens_per_rank*/,
+                  int64_t /*hidden*/, int64_t /*num_topk*/, bool use_fp8_dispatch, bool /*deterministic*/,
+                  bool /*allow_hybrid_mode*/, bool allow_multiple_reduction, bool /*prefer_overlap_with_compute*/,
+                  int /*sl_idx*/, int /*num_allocated_qps*/, int /*num_cpu_timeout_secs*/, int num_gpu_timeout_secs)
+        : Buffer(checked_rank(rank_, use_fp8_dispatch, allow_multiple_reduction), num_ranks_, num_buffer_bytes,
+                 false),
+          rank(rank_),
+          gpu_timeout_secs(num_gpu_timeout_secs) {}
+    // what is not built is refused before anything is allocated
+    static int checked_rank(int rank, bool use_fp8_dispatch, bool allow_multiple_reduction) {
+        if (use_fp8_dispatch) throw std::runtime_error("ElasticBuffer: pre-quantised dispatch is not built");
+        if (!allow_multiple_reduction)
+            throw std::runtime_error("ElasticBuffer supports only allow_multiple_reduction=True");
+        return rank;
+    }
+    static int64_t calculate_buffer_size(int num_ranks, int64_t M, int64_t hidden, int64_t num_topk, bool, bool,
+                                         bool) {
+        return (int64_t)mcep_elastic_buffer_size_hint((int)M, (int)hidden, num_ranks, (int)std::max<int64_t>(num_topk, 1));
+    }
+    std::tuple<int, int> get_physical_domain_size() const { return {1, num_ranks}; }
+    std::tuple<int, int> get_logical_domain_size() const { return {1, num_ranks}; }
+    int get_theoretical_num_sms(int, int) const { return 0; }  // the kernels size their own grids
+    int64_t timeout_us() const { return gpu_timeout_secs < 0 ? -1 : gpu_timeout_secs * 1000000; }
+
+    // mooncake-ep/src/mooncake_ep_elastic_buffer.cpp:230-245 (the hybrid-mode tensors are accepted and unused)
+    std::optional<std::shared_ptr<Event>> dispatch(
+        uint64_t x, int x_element_size, uint64_t sf, int num_tokens, int hidden, int num_sf_packs,
+        int sf_token_stride, int sf_hidden_stride, uint64_t topk_idx, int num_topk, uint64_t topk_weights,
+        uint64_t active_ranks, int num_experts, int num_max_tokens_per_rank, int expert_alignment, int /*num_sms*/,
+        bool do_expand, bool async_with_compute_stream, uint64_t compute_stream, bool cached_mode,
+        uint64_t psum_rank, uint64_t psum_expert, uint64_t dst_buffer_slot_idx, uint64_t /*token_metadata*/,
+        uint64_t /*channel_linked_list*/, uint64_t recv_x, uint64_t recv_x_scales, uint64_t recv_topk_idx,
+        uint64_t recv_topk_weights, uint64_t recv_src_metadata) {
+        mcep_elastic_dispatch_args a = {};
+        a.x = reinterpret_cast<const void*>(x), a.x_element_size = x_element_size;
+        a.sf = reinterpret_cast<const void*>(sf);
+        a.num_tokens = num_tokens, a.hidden = hidden, a.num_sf_packs = num_sf_packs;
+        a.sf_token_stride = sf_token_stride, a.sf_hidden_stride = sf_hidden_stride;
+        a.topk_idx = reinterpret_cast<const int64_t*>(topk_idx), a.num_topk = num_topk;
+        a.topk_weights = reinterpret_cast<const float*>(topk_weights);
+        a.active_ranks = reinterpret_cast<int32_t*>(active_ranks);
+        a.num_experts = num_experts, a.num_max_tokens_per_rank = num_max_tokens_per_rank;
+        a.expert_alignment = expert_alignment, a.do_expand = do_expand ? 1 : 0;
+        a.cached_mode = cached_mode ? 1 : 0, a.timeout_us = timeout_us();
+        a.async_with_compute_stream = async_with_compute_stream ? 1 : 0, a.compute_stream = compute_stream;
+        a.psum_num_recv_tokens_per_scaleup_rank = reinterpret_cast<int32_t*>(psum_rank);
+        a.psum_num_recv_tokens_per_expert = reinterpret_cast<int32_t*>(psum_expert);
+        a.dst_buffer_slot_idx = reinterpret_cast<int32_t*>(dst_buffer_slot_idx);
+        a.recv_x = reinterpret_cast<void*>(recv_x), a.recv_x_scales = reinterpret_cast<void*>(recv_x_scales);
+        a.recv_topk_idx = reinterpret_cast<int64_t*>(recv_topk_idx);
+        a.recv_topk_weights = reinterpret_cast<float*>(recv_topk_weights);
+        a.recv_src_metadata = reinterpret_cast<int32_t*>(recv_src_metadata);
+        a.copied_topk_idx = nullptr;  // the reference's wrapper clones the routing itself
+        mcep_event* ev = nullptr;
+        check(mcep_elastic_dispatch(h, &a, &ev));
+        if (ev) return std::make_shared<Event>(ev);
+        return std::nullopt;
+    }
+
+    // mooncake-ep/src/mooncake_ep_elastic_buffer.cpp:362-370
+    std::optional<std::shared_ptr<Event>> combine(
+        uint64_t x, int num_input_tokens, int hidden, uint64_t topk_idx, int num_combined_tokens, int num_topk,
+        uint64_t topk_weights, uint64_t psum_rank, uint64_t recv_src_metadata, uint64_t /*token_metadata*/,
+        uint64_t /*channel_linked_list*/, uint64_t active_ranks, int num_experts, int num_max_tokens_per_rank,
+        bool do_expand, int /*num_sms*/, bool async_with_compute_stream, uint64_t compute_stream,
+        uint64_t combined_x) {
+        mcep_elastic_combine_args a = {};
+        a.x = reinterpret_cast<const void*>(x), a.num_input_tokens = num_input_tokens, a.hidden = hidden;
+        a.topk_idx = reinterpret_cast<const int64_t*>(topk_idx);
+        a.num_combined_tokens = num_combined_tokens, a.num_topk = num_topk;
+        a.topk_weights = reinterpret_cast<const float*>(topk_weights);
+        a.psum_num_recv_tokens_per_scaleup_rank = reinterpret_cast<const int32_t*>(psum_rank);
+        a.recv_src_metadata = reinterpret_cast<const int32_t*>(recv_src_metadata);
+        a.active_ranks = reinterpret_cast<int32_t*>(active_ranks);
+        a.num_experts = num_experts, a.num_max_tokens_per_rank = num_max_tokens_per_rank;
+        a.do_expand = do_expand ? 1 : 0, a.timeout_us = timeout_us();
+        a.async_with_compute_stream = async_with_compute_stream ? 1 : 0, a.compute_stream = compute_stream;
+        a.combined_x = reinterpret_cast<void*>(combined_x);
+        mcep_event* ev = nullptr;
+        check(mcep_elastic_combine(h, &a, &ev));
+        if (ev) return std::make_shared<Event>(ev);
+        return std::nullopt;
+    }
+};
+
 }  // namespace
 
 PYBIND11_MODULE(_ep, m) {
@@ -193,4 +282,30 @@ PYBIND11_MODULE(_ep, m) {
         .def("combine", &Buffer::combine)
         .def("next_recv_x", &Buffer::next_recv_x)
         .def("next_combine_buffer", &Buffer::next_combine_buffer);
+    m.def("calculate_elastic_buffer_size", &ElasticBuffer::calculate_buffer_size);
+    py::class_<ElasticBuffer>(m, "ElasticBuffer")
+        .def(py::init<int, int, int64_t, int64_t, int64_t, int64_t, bool, bool, bool, bool, bool, int, int, int,
+                      int>(),
+             py::arg("rank"), py::arg("num_ranks"), py::arg("num_buffer_bytes"),
+             py::arg("num_max_tokens_per_rank"), py::arg("hidden"), py::arg("num_topk"),
+             py::arg("use_fp8_dispatch"), py::arg("deterministic"), py::arg("allow_hybrid_mode"),
+             py::arg("allow_multiple_reduction"), py::arg("prefer_overlap_with_compute"), py::arg("sl_idx"),
+             py::arg("num_allocated_qps"), py::arg("num_cpu_timeout_secs"), py::arg("num_gpu_timeout_secs"))
+        .def_static("calculate_buffer_size", &ElasticBuffer::calculate_buffer_size)
+        .def("get_physical_domain_size", &ElasticBuffer::get_physical_domain_size)
+        .def("get_logical_domain_size", &ElasticBuffer::get_logical_domain_size)
+        .def("get_theoretical_num_sms", &ElasticBuffer::get_theoretical_num_sms)
+        .def("ibgda_disabled", &ElasticBuffer::ibgda_disabled)
+        .def("use_fast_path", &ElasticBuffer::use_fast_path)
+        .def("update_local_qpns", &ElasticBuffer::update_local_qpns)
+        .def("is_roce", &ElasticBuffer::is_roce)
+        .def("sync_ibgda_peers", &ElasticBuffer::sync_ibgda_peers)
+        .def("get_mr_info", &ElasticBuffer::get_mr_info)
+        .def("get_gid", &ElasticBuffer::get_gid)
+        .def("get_local_qpns", &ElasticBuffer::get_local_qpns)
+        .def("get_local_lids", &ElasticBuffer::get_local_lids)
+        .def("get_ipc_handle", &ElasticBuffer::get_ipc_handle)
+        .def("sync_nvlink_ipc_handles", &ElasticBuffer::sync_nvlink_ipc_handles)
+        .def("dispatch", &ElasticBuffer::dispatch)
+        .def("combine", &ElasticBuffer::combine);
 }

@@ -106,10 +106,23 @@ def test_pybind_binding_compiles_and_has_the_reference_module_surface(tmp_path):
                  "get_ipc_handle", "sync_nvlink_ipc_handles", "dispatch", "combine"):
         assert hasattr(m.Buffer, name), name
     assert hasattr(m.EventHandle, "current_stream_wait") and hasattr(m.EventHandle, "synchronize")
+    # the elastic class of the same module (mooncake-ep/src/ep_py.cpp:48-87)
+    for name in ("calculate_buffer_size", "get_physical_domain_size", "get_logical_domain_size",
+                 "get_theoretical_num_sms", "ibgda_disabled", "use_fast_path", "update_local_qpns", "is_roce",
+                 "sync_ibgda_peers", "get_mr_info", "get_gid", "get_local_qpns", "get_local_lids",
+                 "get_ipc_handle", "sync_nvlink_ipc_handles", "dispatch", "combine"):
+        assert hasattr(m.ElasticBuffer, name), name
+    assert m.calculate_elastic_buffer_size(8, 128, 4096, 8, False, True, True) == \
+        m.ElasticBuffer.calculate_buffer_size(8, 128, 4096, 8, False, True, True) == \
+        2 * 8 * 128 * (32 + 4 * 4096) + 2 * 8 * 128 * 80
     import torch
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError, match="Failed: CUDA error"):  # loud, no fallback
             m.Buffer(0, 1, 1 << 20)
+        with pytest.raises(RuntimeError, match="Failed: CUDA error"):
+            m.ElasticBuffer(0, 1, 1 << 20, 128, 4096, 8, False, False, True, True, True, 3, 0, 300, 100)
+        with pytest.raises(RuntimeError, match="not built"):
+            m.ElasticBuffer(0, 1, 1 << 20, 128, 4096, 8, True, False, True, True, True, 3, 0, 300, 100)
 
 
 _C_KINDS = {"int32_t": ("i", 4), "int64_t": ("i", 8), "uint64_t": ("u", 8)}

@@ -189,3 +189,47 @@ def test_pybind_binding_drives_a_layer(tmp_path):
         b.dispatch(x.data_ptr(), idx.data_ptr(), active.data_ptr(), T, H, K, T, E, 200_000, False,
                    rx.data_ptr(), 0, cnt.data_ptr(), src_info.data_ptr(), layout_range.data_ptr(),
                    True, True, stream)
+
+
+def test_pybind_elastic_binding_drives_a_layer(tmp_path):
+    """`ElasticBuffer` of the compiled binding in the place of `mooncake._ep.ElasticBuffer`:
+    a dispatch and a combine on a single rank with the argument lists the reference's
+    wrapper passes (mooncake-wheel/mooncake/mooncake_elastic_buffer.py:602-633, 736-756)
+    give what the package's own wrapper gives."""
+    from pybind_build import build_and_import
+    from mooncake_b200 import ElasticBuffer
+    m = build_and_import(str(tmp_path))
+    T, H, E, K = 48, 1024, 16, 4
+    x, idx, w = _inputs(0, T, H, E, K, seed=4)
+    stream = torch.cuda.current_stream().cuda_stream
+    ref = ElasticBuffer(FakeGroup(0, 1), num_max_tokens_per_rank=T, hidden=H, num_topk=K)
+    want_rx, want_idx, want_w, want_h, _ = ref.dispatch(x, topk_idx=idx, topk_weights=w, num_experts=E,
+                                                        num_max_tokens_per_rank=T, do_cpu_sync=True)
+    want_out, _, _ = ref.combine(want_rx.contiguous(), want_h)
+    torch.cuda.synchronize()
+
+    b = m.ElasticBuffer(0, 1, 0, T, H, K, False, False, True, True, True, 3, 0, 300, 10)
+    assert b.ibgda_disabled() and b.use_fast_path() and b.get_logical_domain_size() == (1, 1)
+    active = torch.ones(1, dtype=torch.int32, device="cuda")
+    i32 = lambda *s: torch.empty(s, dtype=torch.int32, device="cuda")  # noqa: E731
+    psum_rank, psum_expert, slot, md = i32(1), i32(E + 1), i32(T, K), i32(T, K + 2)
+    rx = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    ridx = torch.empty((T, K), dtype=torch.int64, device="cuda")
+    rw = torch.empty((T, K), dtype=torch.float32, device="cuda")
+    ev = b.dispatch(x.data_ptr(), 2, 0, T, H, 0, 0, 0, idx.data_ptr(), K, w.data_ptr(), active.data_ptr(), E, T, 1,
+                    24, False, False, stream, False, psum_rank.data_ptr(), psum_expert.data_ptr(),
+                    slot.data_ptr(), 0, 0, rx.data_ptr(), 0, ridx.data_ptr(), rw.data_ptr(), md.data_ptr())
+    assert ev is None
+    out = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    ev = b.combine(rx.data_ptr(), T, H, idx.data_ptr(), T, K, 0, psum_rank.data_ptr(), md.data_ptr(), 0, 0,
+                   active.data_ptr(), E, T, False, 24, True, stream, out.data_ptr())
+    assert ev is not None
+    ev.current_stream_wait(stream)
+    torch.cuda.synchronize()
+    n = int(psum_rank[-1])
+    assert n == want_rx.shape[0]
+    assert torch.equal(rx[:n], want_rx) and torch.equal(ridx[:n], want_idx) and torch.equal(rw[:n], want_w)
+    assert torch.equal(md[:n, :2], want_h.recv_src_metadata[:, :2])
+    assert torch.equal(psum_expert[1:], want_h.psum_num_recv_tokens_per_expert)
+    assert torch.equal(slot, want_h.dst_buffer_slot_idx)
+    assert torch.equal(out.view(torch.int16), want_out.view(torch.int16))
