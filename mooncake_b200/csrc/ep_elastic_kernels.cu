@@ -55,22 +55,46 @@ __device__ __forceinline__ int block_position(bool flag, int* s_warp, int* s_bas
     return pos;
 }
 
-// One block per destination rank r: which tokens go to r, at which lane of their
+// One block per destination rank r and 256 tokens: which tokens go to r, at which lane of their
 // top-k list (the last one that names an expert of r, as `deduplicate` of
 // mooncake_ep_elastic_ptx.cuh:690-693 elects), and in which position (token
 // order, as the deterministic prologue of the reference assigns them:
 // mooncake_ep_elastic_dispatch_deterministic_prologue.cuh:134-166). The block
 // also stores, in rank r's memory, the record of every row r is about to get.
 __global__ void __launch_bounds__(kThreads) ep_elastic_route_kernel(ElasticRouteParams p) {
-    const int r = blockIdx.x;
+    const int r = blockIdx.x;                 // destination rank
+    const int first = blockIdx.y * kThreads;  // this block's 256 tokens
     const int L = p.E / p.R;
     pdl_launch_dependents();  // the exchange's first kernel may take its place; it waits for this one at its top
     __shared__ int s_warp[kWarps];
     __shared__ int s_base;
-    if (threadIdx.x == 0) s_base = 0;
-    __syncthreads();
-    for (int t0 = 0; t0 < p.T; t0 += kThreads) {
-        const int t = t0 + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    {
+        // tokens of the earlier blocks that go to rank r: counted again here (the index matrix
+        // sits in L2) rather than waited for, so no block of this kernel depends on another
+        int before = 0;
+        for (int t = threadIdx.x; t < first; t += kThreads) {
+            bool hit = false;
+#pragma unroll
+            for (int k = 0; k < kMaxTopk; ++k) {
+                if (k >= p.K) break;
+                const int64_t e = __ldg(p.topk_idx + (size_t)t * p.K + k);
+                hit = hit || (e >= 0 && e < p.E && (int)e / L == r);
+            }
+            before += hit ? 1 : 0;
+        }
+        for (int d = 16; d > 0; d >>= 1) before += __shfl_xor_sync(kAll, before, d);
+        if (lane == 0) s_warp[warp] = before;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int sum = 0;
+            for (int i = 0; i < kWarps; ++i) sum += s_warp[i];
+            s_base = sum;
+        }
+        __syncthreads();
+    }
+    {
+        const int t = first + threadIdx.x;
         // the token's choices, all loaded before anything is stored
         int64_t raw[kMaxTopk];
         int rk[kMaxTopk];
@@ -85,7 +109,7 @@ __global__ void __launch_bounds__(kThreads) ep_elastic_route_kernel(ElasticRoute
             }
         }
         const int slot = block_position(master >= 0, s_warp, &s_base);
-        if (t >= p.T) continue;
+        if (t >= p.T) return;
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) {
             if (k >= p.K) break;
@@ -112,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) ep_elastic_route_kernel(ElasticRoute
             }
             reinterpret_cast<int32_t*>(rec)[2 * p.K] = t;
         }
-        if (r != 0 || p.copied_topk_idx == nullptr) continue;
+        if (r != 0 || p.copied_topk_idx == nullptr) return;
 #pragma unroll
         for (int k = 0; k < kMaxTopk; ++k) {
             if (k >= p.K) break;
@@ -321,7 +345,8 @@ __global__ void ep_elastic_fill_ones_kernel(float* w, size_t n) {
 
 cudaError_t launch_elastic_route(const ElasticRouteParams& p, cudaStream_t stream) {
     LaunchScope scope("ep_elastic_route", stream);
-    ep_elastic_route_kernel<<<p.R, kThreads, 0, stream>>>(p);
+    const int chunks = p.T > 0 ? (p.T + kThreads - 1) / kThreads : 1;
+    ep_elastic_route_kernel<<<dim3(p.R, chunks), kThreads, 0, stream>>>(p);
     return scope.done(cudaGetLastError());
 }
 
