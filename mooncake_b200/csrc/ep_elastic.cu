@@ -80,6 +80,7 @@ struct ElasticState {
     // elastic call): a peer may still be reading one call's records while the next call's are
     // being stored, so the two areas must not move with the shapes of the calls.
     size_t record_area_bytes = 0;
+    bool comm_stream_busy = false;  // a call was queued on the communication stream and not yet waited for here
 };
 
 std::mutex g_mu;
@@ -174,10 +175,20 @@ int pick_stream(ElasticState* s, const mcep::BufferView& v, bool async, uint64_t
                 cudaStream_t* out) {
     cudaStream_t compute = reinterpret_cast<cudaStream_t>(compute_stream);
     *out = compute;
-    if (!async) return MCEP_OK;
+    if (!async) {
+        // the calls of a buffer share scratch: one that runs on the caller's stream waits for
+        // what earlier calls left on the communication stream
+        if (s->comm_stream_busy) {
+            EL_CUDA(cudaEventRecord(s->ev, v.comm_stream));
+            EL_CUDA(cudaStreamWaitEvent(compute, s->ev, 0));
+            s->comm_stream_busy = false;
+        }
+        return MCEP_OK;
+    }
     // as the reference: the communication stream, behind everything queued on the caller's
     EL_CUDA(cudaEventRecord(s->ev, compute));
     EL_CUDA(cudaStreamWaitEvent(v.comm_stream, s->ev, 0));
+    s->comm_stream_busy = true;
     *out = v.comm_stream;
     return MCEP_OK;
 }

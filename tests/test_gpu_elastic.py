@@ -216,3 +216,41 @@ def test_elastic_argument_errors():
     with pytest.raises(RuntimeError, match="no more record space"):
         call(M=64)
     torch.cuda.synchronize()
+
+
+def test_asynchronous_call_followed_by_one_on_the_callers_stream():
+    """An asynchronous dispatch (communication stream) and, without waiting for it,
+    a second dispatch on the caller's stream: the calls share scratch, so the
+    second must queue behind the first; both must match the oracle."""
+    from mooncake_b200 import ElasticBuffer
+    from tests.ep_harness import FakeGroup
+    T, H, E, K = 96, 1024, 8, 4
+    buf = ElasticBuffer(FakeGroup(0, 1), num_max_tokens_per_rank=T, hidden=H, num_topk=K, num_gpu_timeout_secs=2)
+    ins = [make_rank_inputs(50 + i, 0, T, H, E, K, "uniform", n_mask=4) for i in range(2)]
+    dev = [[t.cuda() for t in i] for i in ins]
+    busy = torch.empty(64 << 20, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        busy.zero_()  # something ahead of the first call on the caller's stream
+    ra, ia, wa, ha, eva = buf.dispatch(dev[0][0], topk_idx=dev[0][1], topk_weights=dev[0][2], num_experts=E,
+                                       num_max_tokens_per_rank=T, do_cpu_sync=False,
+                                       async_with_compute_stream=True)
+    rb, ib, wb, hb, _ = buf.dispatch(dev[1][0], topk_idx=dev[1][1], topk_weights=dev[1][2], num_experts=E,
+                                     num_max_tokens_per_rank=T, do_cpu_sync=False)
+    eva.current_stream_wait()
+    torch.cuda.synchronize()
+    for (r, i, w, h), (x, idx, wt) in (((ra, ia, wa, ha), ins[0]), ((rb, ib, wb, hb), ins[1])):
+        want = eo.elastic_dispatch([x], [idx], [wt], E, T)[0]
+        n = want["n"]
+        assert int(h.psum_num_recv_tokens_per_scaleup_rank[-1]) == n
+        assert torch.equal(r[:n].cpu().view(torch.int16), want["recv_x"].view(torch.int16))
+        assert torch.equal(i[:n].cpu(), want["recv_topk_idx"]) and torch.equal(w[:n].cpu(), want["recv_topk_weights"])
+        assert h.psum_num_recv_tokens_per_expert.cpu().tolist() == want["psum_expert"].tolist()[1:]
+    oa, _, evc = buf.combine(ra, ha, async_with_compute_stream=True)
+    ob, _, _ = buf.combine(rb, hb)
+    evc.current_stream_wait()
+    torch.cuda.synchronize()
+    for o, r, (x, idx, wt) in ((oa, ra, ins[0]), (ob, rb, ins[1])):
+        want = eo.elastic_dispatch([x], [idx], [wt], E, T)
+        ref = eo.elastic_combine([want[0]["recv_x"]], want, [idx], E)[0]
+        assert torch.equal(o.cpu().view(torch.int16), ref.view(torch.int16))
+    assert buf.runtime.status() == 0
