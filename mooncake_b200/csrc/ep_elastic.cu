@@ -47,6 +47,10 @@ using mcep::report_failure;
 
 size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// The record areas end where the data area ends, rounded down so that they stay
+// 16-byte aligned whatever size the caller gave the buffer.
+size_t usable_bytes(int64_t num_bytes) { return num_bytes > 0 ? (size_t)num_bytes / 16 * 16 : 0; }
+
 int record_stride(int K) { return (int)up(8 * (size_t)K + 4, 16); }
 size_t record_bytes(int R, int M, int K) { return up((size_t)R * M * record_stride(K), 256); }
 
@@ -159,7 +163,7 @@ int refresh_record_table(ElasticState* s, const mcep::BufferView& v, int par, si
         if (!v.group)
             want[r] = s->own_records[par];
         else if (v.peer_host[r] != nullptr)
-            want[r] = static_cast<char*>(v.peer_host[r]) + v.data_off + (size_t)v.num_bytes -
+            want[r] = static_cast<char*>(v.peer_host[r]) + v.data_off + usable_bytes(v.num_bytes) -
                       (size_t)(par + 1) * rec_bytes;
     }
     bool same = true;
@@ -217,7 +221,7 @@ extern "C" {
 
 uint64_t mcep_elastic_buffer_size_hint(int M, int hidden, int num_ranks, int num_topk) {
     if (M <= 0 || hidden <= 0 || num_ranks <= 0 || num_topk <= 0) return 0;
-    return mcep::exchange_bytes(num_ranks, num_ranks, M, hidden) + 2 * record_bytes(num_ranks, M, num_topk);
+    return up(mcep::exchange_bytes(num_ranks, num_ranks, M, hidden) + 2 * record_bytes(num_ranks, M, num_topk), 256);
 }
 
 int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, mcep_event** out_event) {
@@ -244,7 +248,7 @@ int mcep_elastic_dispatch(mcep_buffer* b, const mcep_elastic_dispatch_args* a, m
         return report_failure(MCEP_ERR_INVALID,
                               "Failed: Assertion error 'elastic calls of one buffer need no more record "
                               "space (num_max_tokens_per_rank, num_topk) than its first elastic call'");
-    if (v.group && mcep::exchange_bytes(R, R, M, H) + 2 * rec_bytes > (size_t)v.num_bytes) {
+    if (v.group && mcep::exchange_bytes(R, R, M, H) + 2 * rec_bytes > usable_bytes(v.num_bytes)) {
         char m[256];
         snprintf(m, sizeof(m),
                  "Failed: Assertion error %s:%d 'elastic layout fits num_ep_buffer_bytes' (need %zu, have %lld)",

@@ -254,3 +254,16 @@ def test_asynchronous_call_followed_by_one_on_the_callers_stream():
         ref = eo.elastic_combine([want[0]["recv_x"]], want, [idx], E)[0]
         assert torch.equal(o.cpu().view(torch.int16), ref.view(torch.int16))
     assert buf.runtime.status() == 0
+
+
+def test_buffer_of_an_odd_size_keeps_the_records_aligned():
+    """A buffer a few bytes larger than the hint (not a multiple of 16): the record
+    areas are placed from the rounded-down end, the calls work as usual."""
+    R, T, H, E, K, M = 2, 24, 256, 8, 4, 32
+    bufs = local_group(R, ep.elastic_buffer_size_hint(M, H, R, K) + 13, force_staged=True)
+    ins = [make_rank_inputs(61, r, T, H, E, K, "uniform", n_mask=2) for r in range(R)]
+    xs, idxs, ws = [i[0] for i in ins], [i[1] for i in ins], [i[2] for i in ins]
+    keep = []
+    outs = _dispatch(bufs, xs, idxs, ws, E, M, 1, False, keep)
+    _check_dispatch(outs, eo.elastic_dispatch(xs, idxs, ws, E, M), False, True, K)
+    assert all(b.runtime.status() == 0 for b in bufs)
